@@ -1,0 +1,355 @@
+// Row-split CSR SpMM for sm_100a:  C = beta*C + A*B,  fp32 values, int32 indices, row-major B and C.
+//
+// Work decomposition
+//   * one warp per CSR row for ordinary rows; the warp reads the row's (col, val) pairs 32 at a
+//     time with one coalesced load per array and hands them round with warp shuffles;
+//   * LPN lanes cover one gathered row of B with VEC-wide vectors (VEC = 4 -> 128-bit loads), so a
+//     warp works on 32/LPN nonzeros at once: narrow B (f = 16) keeps all 32 lanes busy;
+//   * NV vectors per lane make a feature tile of LPN*VEC*NV columns; wider B is covered by
+//     gridDim.y tiles, dispatched tile-major so that one column slab of B stays hot in L2;
+//   * rows longer than the plan's threshold (power-law hubs) are taken out of the warp-per-row
+//     pass and processed by a whole 512-thread block each, 16 warps on disjoint nonzero ranges,
+//     combined through shared memory in warp order.
+// Every output element is produced by a fixed sequence of operations: results are bit-reproducible
+// run to run, no floating-point atomics anywhere.
+#include <limits.h>
+
+#include "common.cuh"
+
+namespace cagnet {
+
+struct Tuning {
+  int spmm_nv = 0;       // 0 = automatic
+  int spmm_long = 4096;  // rows with more nonzeros go to the block-per-row kernel
+};
+static Tuning g_tuning;
+
+constexpr int kPlanMagic = 0x0CA67E70;
+constexpr int kPlanHeaderInts = 8;   // [0] magic [1] count [2] threshold [3] capacity
+constexpr int kMinLongThreshold = 256;
+constexpr int kLongWarps = 16;
+
+// ------------------------------------------------------------------------------------------------
+template <int VEC>
+__device__ __forceinline__ void load_vec(const float* __restrict__ p, float (&x)[VEC]) {
+  if constexpr (VEC == 4) {
+    const float4 t = __ldg(reinterpret_cast<const float4*>(p));
+    x[0] = t.x; x[1] = t.y; x[2] = t.z; x[3] = t.w;
+  } else if constexpr (VEC == 2) {
+    const float2 t = __ldg(reinterpret_cast<const float2*>(p));
+    x[0] = t.x; x[1] = t.y;
+  } else {
+    x[0] = __ldg(p);
+  }
+}
+
+template <int VEC>
+__device__ __forceinline__ void store_vec(float* p, const float (&x)[VEC]) {
+  if constexpr (VEC == 4) {
+    *reinterpret_cast<float4*>(p) = make_float4(x[0], x[1], x[2], x[3]);
+  } else if constexpr (VEC == 2) {
+    *reinterpret_cast<float2*>(p) = make_float2(x[0], x[1]);
+  } else {
+    *p = x[0];
+  }
+}
+
+// Accumulates sum_e val[e] * B[col[e], tile columns of this lane] over e in [start, end) into acc.
+// bt already points at column (tile0 + l*VEC) of row 0 of B; vector k of the lane sits
+// k*LPN*VEC columns further on and is live iff k < nvalid.
+template <int VEC, int LPN, int NV>
+__device__ __forceinline__ void accumulate_range(const int* __restrict__ col, const float* __restrict__ val,
+                                                 int start, int end, const float* __restrict__ bt, int64_t ldb,
+                                                 int nvalid, int lane, float (&acc)[NV][VEC]) {
+  constexpr int G = 32 / LPN;                      // nonzeros in flight per warp step
+  constexpr int UNROLL = (NV >= 4) ? 2 : (NV >= 2 ? 4 : 8);
+  const int sub = lane / LPN;
+  for (int base = start; base < end; base += 32) {
+    const int e = base + lane;
+    int c = 0;
+    float v = 0.f;
+    if (e < end) {
+      c = __ldg(col + e);
+      v = __ldg(val + e);
+    }
+    const int cnt = min(32, end - base);
+    if (cnt == 32) {
+#pragma unroll UNROLL
+      for (int s = 0; s < 32; s += G) {
+        const int cc = __shfl_sync(0xffffffffu, c, s + sub);
+        const float vv = __shfl_sync(0xffffffffu, v, s + sub);
+        const float* bp = bt + static_cast<int64_t>(cc) * ldb;
+#pragma unroll
+        for (int k = 0; k < NV; ++k) {
+          if (k < nvalid) {
+            float x[VEC];
+            load_vec<VEC>(bp + k * (LPN * VEC), x);
+#pragma unroll
+            for (int j = 0; j < VEC; ++j) acc[k][j] = fmaf(vv, x[j], acc[k][j]);
+          }
+        }
+      }
+    } else {
+      for (int s = 0; s < cnt; s += G) {
+        const int cc = __shfl_sync(0xffffffffu, c, (s + sub) & 31);
+        const float vv = __shfl_sync(0xffffffffu, v, (s + sub) & 31);
+        if (s + sub < cnt) {
+          const float* bp = bt + static_cast<int64_t>(cc) * ldb;
+#pragma unroll
+          for (int k = 0; k < NV; ++k) {
+            if (k < nvalid) {
+              float x[VEC];
+              load_vec<VEC>(bp + k * (LPN * VEC), x);
+#pragma unroll
+              for (int j = 0; j < VEC; ++j) acc[k][j] = fmaf(vv, x[j], acc[k][j]);
+            }
+          }
+        }
+      }
+    }
+  }
+  // fold the 32/LPN nonzero slots of the warp together; afterwards every lane holds the row sums
+#pragma unroll
+  for (int off = LPN; off < 32; off <<= 1) {
+#pragma unroll
+    for (int k = 0; k < NV; ++k)
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) acc[k][j] += __shfl_xor_sync(0xffffffffu, acc[k][j], off);
+  }
+}
+
+// live vectors of lane l in feature tile `tile`: columns tile0 + (k*LPN + l)*VEC < f_eff
+template <int VEC, int LPN, int NV>
+__device__ __forceinline__ int live_vectors(int tile0, int l, int f_eff) {
+  const int first = tile0 + l * VEC;
+  if (first >= f_eff) return 0;
+  return min(NV, (f_eff - first + LPN * VEC - 1) / (LPN * VEC));
+}
+
+template <int VEC, int LPN, int NV>
+__global__ void __launch_bounds__(256) spmm_warp_rows_kernel(const int* __restrict__ rowptr, const int* __restrict__ col,
+                                                             const float* __restrict__ val, int n,
+                                                             const float* __restrict__ B, int64_t ldb,
+                                                             float* __restrict__ C, int64_t ldc, int f_eff, float beta,
+                                                             const int* __restrict__ plan) {
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= n) return;
+  const int lane = threadIdx.x & 31;
+  const int l = lane % LPN;
+  const int tile0 = blockIdx.y * (LPN * VEC * NV);
+  const int start = __ldg(rowptr + row);
+  const int end = __ldg(rowptr + row + 1);
+  const int long_threshold = plan ? __ldg(plan + 2) : INT_MAX;
+  if (end - start > long_threshold) return;  // a hub row: the block-per-row kernel owns it
+  const int nvalid = live_vectors<VEC, LPN, NV>(tile0, l, f_eff);
+
+  float acc[NV][VEC];
+#pragma unroll
+  for (int k = 0; k < NV; ++k)
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) acc[k][j] = 0.f;
+
+  accumulate_range<VEC, LPN, NV>(col, val, start, end, B + tile0 + l * VEC, ldb, nvalid, lane, acc);
+
+  if (lane < LPN) {
+    float* cp = C + static_cast<int64_t>(row) * ldc + tile0 + l * VEC;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      if (k < nvalid) {
+        if (beta != 0.f) {
+          float old[VEC];
+          load_vec<VEC>(cp + k * (LPN * VEC), old);
+#pragma unroll
+          for (int j = 0; j < VEC; ++j) acc[k][j] += old[j];
+        }
+        store_vec<VEC>(cp + k * (LPN * VEC), acc[k]);
+      }
+    }
+  }
+}
+
+template <int VEC, int LPN, int NV>
+__global__ void __launch_bounds__(kLongWarps * 32) spmm_block_rows_kernel(const int* __restrict__ rowptr,
+                                                                          const int* __restrict__ col,
+                                                                          const float* __restrict__ val,
+                                                                          const float* __restrict__ B, int64_t ldb,
+                                                                          float* __restrict__ C, int64_t ldc, int f_eff,
+                                                                          float beta, const int* __restrict__ plan) {
+  constexpr int TILE = LPN * VEC * NV;
+  __shared__ float part[kLongWarps][TILE];
+  const int count = min(__ldg(plan + 1), __ldg(plan + 3));
+  const int* list = plan + kPlanHeaderInts;
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int l = lane % LPN;
+  const int tile0 = blockIdx.y * TILE;
+  const int nvalid = live_vectors<VEC, LPN, NV>(tile0, l, f_eff);
+
+  for (int item = blockIdx.x; item < count; item += gridDim.x) {
+    const int row = __ldg(list + item);
+    const int start = __ldg(rowptr + row);
+    const int end = __ldg(rowptr + row + 1);
+    const int per = (((end - start) + kLongWarps - 1) / kLongWarps + 31) & ~31;
+    const int ws = min(end, start + warp * per);
+    const int we = min(end, ws + per);
+
+    float acc[NV][VEC];
+#pragma unroll
+    for (int k = 0; k < NV; ++k)
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) acc[k][j] = 0.f;
+    accumulate_range<VEC, LPN, NV>(col, val, ws, we, B + tile0 + l * VEC, ldb, nvalid, lane, acc);
+
+    if (lane < LPN) {
+#pragma unroll
+      for (int k = 0; k < NV; ++k)
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) part[warp][(k * LPN + l) * VEC + j] = acc[k][j];
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < TILE; idx += blockDim.x) {
+      const int column = tile0 + idx;
+      if (column < f_eff) {
+        float s = part[0][idx];
+#pragma unroll
+        for (int w = 1; w < kLongWarps; ++w) s += part[w][idx];
+        float* cp = C + static_cast<int64_t>(row) * ldc + column;
+        if (beta != 0.f) s += *cp;
+        *cp = s;
+      }
+    }
+    __syncthreads();
+  }
+}
+
+__global__ void spmm_plan_kernel(const int* __restrict__ rowptr, int n, int threshold, int capacity, int* plan) {
+  const int row = blockIdx.x * blockDim.x + threadIdx.x;
+  if (row >= n) return;
+  if (rowptr[row + 1] - rowptr[row] > threshold) {
+    const int slot = atomicAdd(plan + 1, 1);
+    if (slot < capacity) plan[kPlanHeaderInts + slot] = row;
+  }
+}
+
+__global__ void spmm_plan_header_kernel(int threshold, int capacity, int* plan) {
+  plan[0] = kPlanMagic;
+  plan[1] = 0;
+  plan[2] = threshold;
+  plan[3] = capacity;
+}
+
+static int plan_capacity(int64_t nnz, int threshold) { return static_cast<int>(nnz / threshold) + 1; }
+
+template <int VEC, int LPN, int NV>
+static int launch_spmm(const int* rowptr, const int* col, const float* val, int n, int64_t nnz, const float* B,
+                       int64_t ldb, float* C, int64_t ldc, int f_eff, float beta, const int* plan,
+                       cudaStream_t stream) {
+  constexpr int TILE = LPN * VEC * NV;
+  const int tiles = (f_eff + TILE - 1) / TILE;
+  if (plan) {
+    // grid-stride over the listed rows, so any grid size is correct; this one is tight for the
+    // current threshold and never below one wave
+    const int blocks = max(1, min(plan_capacity(nnz, max(g_tuning.spmm_long, kMinLongThreshold)), 16 * kNumSMs));
+    spmm_block_rows_kernel<VEC, LPN, NV><<<dim3(blocks, tiles), kLongWarps * 32, 0, stream>>>(
+        rowptr, col, val, B, ldb, C, ldc, f_eff, beta, plan);
+  }
+  const int rows_per_block = 8;
+  spmm_warp_rows_kernel<VEC, LPN, NV><<<dim3((n + rows_per_block - 1) / rows_per_block, tiles), rows_per_block * 32, 0,
+                                        stream>>>(rowptr, col, val, n, B, ldb, C, ldc, f_eff, beta, plan);
+  return check_launch("cagnet_spmm_csr_f32");
+}
+
+template <int VEC>
+static int dispatch_shape(int vectors, const int* rowptr, const int* col, const float* val, int n, int64_t nnz,
+                          const float* B, int64_t ldb, float* C, int64_t ldc, int f_eff, float beta, const int* plan,
+                          cudaStream_t stream) {
+#define CAGNET_SPMM_CASE(LPN, NV) \
+  return launch_spmm<VEC, LPN, NV>(rowptr, col, val, n, nnz, B, ldb, C, ldc, f_eff, beta, plan, stream)
+  if (vectors <= 4) CAGNET_SPMM_CASE(4, 1);
+  if (vectors <= 8) CAGNET_SPMM_CASE(8, 1);
+  if (vectors <= 16) CAGNET_SPMM_CASE(16, 1);
+  int nv = g_tuning.spmm_nv;
+  if (nv <= 0) nv = vectors <= 160 ? (vectors + 31) / 32 : 4;
+  nv = min(nv, (vectors + 31) / 32);
+  switch (nv) {
+    case 1: CAGNET_SPMM_CASE(32, 1);
+    case 2: CAGNET_SPMM_CASE(32, 2);
+    case 3: CAGNET_SPMM_CASE(32, 3);
+    case 4: CAGNET_SPMM_CASE(32, 4);
+    default: CAGNET_SPMM_CASE(32, 5);
+  }
+#undef CAGNET_SPMM_CASE
+}
+
+}  // namespace cagnet
+
+using namespace cagnet;
+
+extern "C" int cagnet_set_param(const char* name, int value) {
+  if (!name) return fail(CAGNET_E_ARG, "cagnet_set_param: null name");
+  if (!strcmp(name, "spmm_nv")) {
+    if (value < 0 || value > 5) return fail(CAGNET_E_ARG, "cagnet_set_param: spmm_nv must be in [0, 5]");
+    g_tuning.spmm_nv = value;
+    return CAGNET_OK;
+  }
+  if (!strcmp(name, "spmm_long")) {
+    if (value < kMinLongThreshold) return fail(CAGNET_E_ARG, "cagnet_set_param: spmm_long must be >= 256");
+    g_tuning.spmm_long = value;
+    return CAGNET_OK;
+  }
+  return fail(CAGNET_E_ARG, "cagnet_set_param: unknown parameter '%s'", name);
+}
+
+extern "C" int cagnet_get_param(const char* name) {
+  if (name && !strcmp(name, "spmm_nv")) return g_tuning.spmm_nv;
+  if (name && !strcmp(name, "spmm_long")) return g_tuning.spmm_long;
+  return -1;
+}
+
+extern "C" size_t cagnet_spmm_plan_bytes(int32_t n, int64_t nnz) {
+  (void)n;
+  if (nnz < 0) return 0;
+  return sizeof(int) * (kPlanHeaderInts + static_cast<size_t>(plan_capacity(nnz, kMinLongThreshold)));
+}
+
+extern "C" int cagnet_spmm_plan_i32(const int32_t* rowptr, int32_t n, int64_t nnz, void* plan, size_t plan_bytes,
+                                    void* stream) {
+  if (!rowptr || !plan || n < 0 || nnz < 0) return fail(CAGNET_E_ARG, "cagnet_spmm_plan_i32: bad argument");
+  if (nnz > INT_MAX) return fail(CAGNET_E_OVERFLOW, "cagnet_spmm_plan_i32: nnz %s%lld exceeds int32", "", nnz);
+  if (plan_bytes < cagnet_spmm_plan_bytes(n, nnz))
+    return fail(CAGNET_E_WORKSPACE, "cagnet_spmm_plan_i32: plan buffer of %s%lld bytes is too small (need %lld)", "",
+                (long long)plan_bytes, (long long)cagnet_spmm_plan_bytes(n, nnz));
+  if (!aligned(plan, 16)) return fail(CAGNET_E_ALIGN, "cagnet_spmm_plan_i32: plan buffer must be 16-byte aligned");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int threshold = g_tuning.spmm_long;
+  const int capacity = plan_capacity(nnz, threshold);
+  spmm_plan_header_kernel<<<1, 1, 0, s>>>(threshold, capacity, static_cast<int*>(plan));
+  if (n > 0) spmm_plan_kernel<<<(n + 255) / 256, 256, 0, s>>>(rowptr, n, threshold, capacity, static_cast<int*>(plan));
+  return check_launch("cagnet_spmm_plan_i32");
+}
+
+extern "C" int cagnet_spmm_csr_f32(const int32_t* rowptr, const int32_t* col, const float* val, int32_t n, int32_t m,
+                                   int64_t nnz, const float* B, int64_t ldb, float* C, int64_t ldc, int32_t f,
+                                   float beta, const void* plan, void* stream) {
+  if (n < 0 || m < 0 || nnz < 0 || f < 0) return fail(CAGNET_E_ARG, "cagnet_spmm_csr_f32: negative size");
+  if (n == 0 || f == 0) return CAGNET_OK;
+  if (!rowptr || !C || (nnz > 0 && (!col || !val || !B)))
+    return fail(CAGNET_E_ARG, "cagnet_spmm_csr_f32: null pointer");
+  if (beta != 0.f && beta != 1.f) return fail(CAGNET_E_ARG, "cagnet_spmm_csr_f32: beta must be 0 or 1");
+  if (nnz > INT_MAX) return fail(CAGNET_E_OVERFLOW, "cagnet_spmm_csr_f32: nnz %s%lld exceeds int32", "", nnz);
+  if (ldb < f || ldc < f)
+    return fail(CAGNET_E_ALIGN, "cagnet_spmm_csr_f32: leading dimension%s (%lld, %lld) smaller than f", "", ldb, ldc);
+  if (!B) B = C;  // nnz == 0: never dereferenced
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int* p = static_cast<const int*>(plan);
+  auto round_up = [](int x, int a) { return (x + a - 1) / a * a; };
+  if (ldb % 4 == 0 && ldc % 4 == 0 && aligned(B, 16) && aligned(C, 16) && round_up(f, 4) <= ldb && round_up(f, 4) <= ldc) {
+    const int f_eff = round_up(f, 4);
+    return dispatch_shape<4>(f_eff / 4, rowptr, col, val, n, nnz, B, ldb, C, ldc, f_eff, beta, p, s);
+  }
+  if (ldb % 2 == 0 && ldc % 2 == 0 && aligned(B, 8) && aligned(C, 8) && round_up(f, 2) <= ldb && round_up(f, 2) <= ldc) {
+    const int f_eff = round_up(f, 2);
+    return dispatch_shape<2>(f_eff / 2, rowptr, col, val, n, nnz, B, ldb, C, ldc, f_eff, beta, p, s);
+  }
+  return dispatch_shape<1>(f, rowptr, col, val, n, nnz, B, ldb, C, ldc, f, beta, p, s);
+}

@@ -1,0 +1,278 @@
+"""Torch-facing wrappers of the C ABI: device tensors in, kernels launched on the current stream.
+
+Mirrors the reference's native operator surface (`sparse_coo_tensor_cpp.spmm_gpu`,
+`sparse_coo_tensor_cpp.sparse_coo_tensor_gpu`; sparse-extension/sparse_coo_tensor.cu:43-54, 113-240)
+and adds the cached-CSR form the GCN layers use.  PyTorch is only the owner of device memory and
+streams here; every computation is a kernel of `libcagnet_b200.so`.  CPU tensors are rejected.
+"""
+import torch
+
+from . import _native
+
+EPI_NONE, EPI_RELU, EPI_LOG_SOFTMAX, EPI_RELU_MASK = 0, 1, 2, 3
+_INT32_MAX = 2 ** 31 - 1
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def pad_ld(f):
+    """Leading dimension used for matrices this package allocates: rows start on a 16-byte boundary
+    (128-bit loads) and, for wide rows, on a 128-byte cache line."""
+    return (f + 3) // 4 * 4 if f <= 64 else (f + 31) // 32 * 32
+
+
+def empty_padded(n, f, device):
+    """n x f fp32 view with stride (pad_ld(f), 1); `.base_buffer()` of it is the contiguous n x ld buffer."""
+    buf = torch.empty((n, pad_ld(f)), dtype=torch.float32, device=device)
+    return buf[:, :f]
+
+
+def zeros_padded(n, f, device):
+    buf = torch.zeros((n, pad_ld(f)), dtype=torch.float32, device=device)
+    return buf[:, :f]
+
+
+def to_padded(x):
+    """Copy of x (n x f) in the padded layout (pad columns zero)."""
+    out = zeros_padded(x.size(0), x.size(1), x.device)
+    out.copy_(x)
+    return out
+
+
+def base_buffer(view):
+    """The contiguous n x ld buffer behind a padded view (what a collective must move), or the view
+    itself when it is already contiguous."""
+    if view.is_contiguous():
+        return view
+    base = view._base
+    if base is not None and base.dim() == 2 and base.is_contiguous() and base.size(0) == view.size(0) \
+            and base.data_ptr() == view.data_ptr() and base.size(1) == view.stride(0):
+        return base
+    raise RuntimeError("cagnet_b200: tensor is neither contiguous nor a padded view")
+
+
+def _ld(t, name):
+    if not t.is_cuda:
+        raise RuntimeError("cagnet_b200: %s must be a CUDA tensor (there is no CPU path)" % name)
+    if t.dtype != torch.float32 or t.dim() != 2:
+        raise RuntimeError("cagnet_b200: %s must be a 2-D float32 tensor" % name)
+    rows, cols = t.shape
+    if cols > 1 and t.stride(1) != 1:
+        raise RuntimeError("cagnet_b200: %s must be row-major (unit column stride)" % name)
+    if rows > 1:
+        if t.stride(0) < cols:
+            raise RuntimeError("cagnet_b200: %s has overlapping rows" % name)
+        return t.stride(0)
+    return max(cols, 1)
+
+
+def _row_major(t):
+    return t.dim() == 2 and (t.size(1) <= 1 or t.stride(1) == 1) and (t.size(0) <= 1 or t.stride(0) >= t.size(1))
+
+
+# ------------------------------------------------------------------------------------------ sparse
+def coo2csr(rows, n):
+    """rowptr[i] = #{e : rows[e] < i} for sorted int32 row indices on the device (int32, n + 1 entries)."""
+    if not rows.is_cuda or rows.dtype != torch.int32 or rows.dim() != 1:
+        raise RuntimeError("cagnet_b200: coo2csr needs a 1-D int32 CUDA tensor")
+    rows = rows.contiguous()
+    rowptr = torch.empty(n + 1, dtype=torch.int32, device=rows.device)
+    with torch.cuda.device(rows.device):
+        _native.check(_native.lib().cagnet_coo2csr_i32(rows.data_ptr(), rows.numel(), n, rowptr.data_ptr(), _stream()),
+                      "coo2csr")
+    return rowptr
+
+
+class CsrBlock:
+    """A static n x m sparse block on the device: int32 CSR + fp32 values + the SpMM plan (list of hub rows).
+
+    Built once per adjacency block at partition time; the reference instead rebuilds the CSR offsets
+    inside every `spmm_gpu` call (sparse_coo_tensor.cu:136-142)."""
+
+    def __init__(self, rowptr, col, val, n, m, plan=None):
+        self.rowptr, self.col, self.val, self.n, self.m, self.plan = rowptr, col, val, int(n), int(m), plan
+        self.nnz = int(val.numel())
+
+    @staticmethod
+    def from_coo(rows, cols, vals, n, m, validate=True, plan=True):
+        """rows/cols: integer tensors sorted by row (a coalesced COO), vals fp32; any device (moved to CUDA)."""
+        if n > _INT32_MAX or m > _INT32_MAX or vals.numel() > _INT32_MAX:
+            raise RuntimeError("cagnet_b200: block does not fit 32-bit indices")
+        dev = vals.device if vals.is_cuda else torch.device("cuda", torch.cuda.current_device())
+        rows32 = rows.to(device=dev, dtype=torch.int32).contiguous()
+        col32 = cols.to(device=dev, dtype=torch.int32).contiguous()
+        val = vals.to(device=dev, dtype=torch.float32).contiguous()
+        rowptr = coo2csr(rows32, n)
+        blk = CsrBlock(rowptr, col32, val, n, m)
+        if validate:
+            blk.validate()
+        if plan:
+            blk.build_plan()
+        return blk
+
+    def validate(self):
+        status = torch.zeros(1, dtype=torch.int32, device=self.val.device)
+        with torch.cuda.device(self.val.device):
+            _native.check(_native.lib().cagnet_check_csr_i32(self.rowptr.data_ptr(), self.col.data_ptr(), self.n, self.m,
+                                                             self.nnz, status.data_ptr(), _stream()), "check_csr")
+        code = int(status.item())
+        if code:
+            reason = {1: "rowptr[0] != 0", 2: "rowptr[n] != nnz (row index out of range or unsorted)",
+                      3: "row indices not sorted", 4: "column index out of range"}.get(code, "?")
+            raise RuntimeError("cagnet_b200: malformed sparse block: " + reason)
+
+    def build_plan(self):
+        nbytes = _native.lib().cagnet_spmm_plan_bytes(self.n, self.nnz)
+        self.plan = torch.empty((nbytes + 15) // 16 * 16, dtype=torch.uint8, device=self.val.device)
+        with torch.cuda.device(self.val.device):
+            _native.check(_native.lib().cagnet_spmm_plan_i32(self.rowptr.data_ptr(), self.n, self.nnz,
+                                                             self.plan.data_ptr(), self.plan.numel(), _stream()),
+                          "spmm_plan")
+
+    def long_rows(self):
+        """Number of rows the plan routes to the block-per-row kernel (synchronises)."""
+        return 0 if self.plan is None else int(self.plan[4:8].view(torch.int32).item())
+
+    def bytes_alg(self, f, beta):
+        """Algorithmic HBM bytes of one multiply by an m x f matrix: offsets + (col, val) streams + B read once
+        + C written (and read when accumulating)."""
+        return 4 * (self.n + 1) + 8 * self.nnz + 4 * self.m * f + 4 * self.n * f * (1 + int(beta != 0))
+
+
+def spmm(block, B, C, beta=1.0):
+    """C = beta * C + block @ B in place (beta 0 or 1)."""
+    ldb, ldc = _ld(B, "B"), _ld(C, "C")
+    if B.size(0) != block.m or C.size(0) != block.n or B.size(1) != C.size(1):
+        raise RuntimeError("cagnet_b200: spmm shape mismatch: A %dx%d, B %s, C %s"
+                           % (block.n, block.m, tuple(B.shape), tuple(C.shape)))
+    if B.device != block.val.device or C.device != block.val.device:
+        raise RuntimeError("cagnet_b200: spmm operands on different devices")
+    with torch.cuda.device(C.device):
+        _native.check(_native.lib().cagnet_spmm_csr_f32(
+            block.rowptr.data_ptr(), block.col.data_ptr(), block.val.data_ptr(), block.n, block.m, block.nnz,
+            B.data_ptr(), ldb, C.data_ptr(), ldc, B.size(1), float(beta),
+            None if block.plan is None else block.plan.data_ptr(), _stream()), "spmm")
+    return C
+
+
+def spmm_gpu(A_rowindices, A_colindices, A_values, n, m, B, C):
+    """Drop-in for `sparse_coo_tensor_cpp.spmm_gpu` (sparse_coo_tensor.cu:113-119): C += A.B in place, A given
+    as row-sorted COO with int32 indices.  Value semantics only: strides of B and C are left untouched, there
+    is no device-wide synchronisation, and the work is queued on the current stream."""
+    if A_rowindices.dtype != torch.int32 or A_colindices.dtype != torch.int32:
+        raise RuntimeError("cagnet_b200: spmm_gpu expects int32 indices (call .int() as the reference does)")
+    if n > _INT32_MAX or m > _INT32_MAX:
+        raise RuntimeError("cagnet_b200: spmm_gpu block does not fit 32-bit indices")
+    block = CsrBlock(coo2csr(A_rowindices, n), A_colindices.contiguous(), A_values.float().contiguous(), n, m)
+    block.build_plan()
+    Bc = B if _row_major(B) else B.contiguous()
+    if _row_major(C):
+        spmm(block, Bc, C, 1.0)
+    else:  # e.g. the column-major-strided views the reference's own op leaves behind
+        tmp = C.contiguous()
+        spmm(block, Bc, tmp, 1.0)
+        C.copy_(tmp)
+
+
+def sparse_coo_tensor_gpu(indices, values, size):
+    """Drop-in for `sparse_coo_tensor_cpp.sparse_coo_tensor_gpu` (sparse_coo_tensor.cu:43-54): sparse COO
+    constructor without index validation (and so without a device synchronisation)."""
+    return torch._sparse_coo_tensor_unsafe(indices, values, tuple(size))
+
+
+# ------------------------------------------------------------------------------------------- dense
+def gemm_nn(X, W, trans_w=False, epilogue=EPI_NONE, aux=None, out=None):
+    """epilogue(X @ W) (or X @ W.T when trans_w) for tall X and a small W; result in the padded layout."""
+    ldx, ldw = _ld(X, "X"), _ld(W, "W")
+    K = X.size(1)
+    if trans_w:
+        N = W.size(0)
+        if W.size(1) != K:
+            raise RuntimeError("cagnet_b200: gemm_nn shape mismatch %s x %s^T" % (tuple(X.shape), tuple(W.shape)))
+    else:
+        N = W.size(1)
+        if W.size(0) != K:
+            raise RuntimeError("cagnet_b200: gemm_nn shape mismatch %s x %s" % (tuple(X.shape), tuple(W.shape)))
+    if out is None:
+        out = empty_padded(X.size(0), N, X.device)
+    ldz = _ld(out, "out")
+    aux_ptr, ldaux = (None, 0) if aux is None else (aux.data_ptr(), _ld(aux, "aux"))
+    with torch.cuda.device(X.device):
+        _native.check(_native.lib().cagnet_gemm_nn_f32(X.data_ptr(), ldx, W.data_ptr(), ldw, int(bool(trans_w)),
+                                                       out.data_ptr(), ldz, X.size(0), K, N, int(epilogue), aux_ptr,
+                                                       ldaux, _stream()), "gemm_nn")
+    return out
+
+
+def gemm_tn(H, G):
+    """H.T @ G for tall H (n x K) and G (n x N): K x N contiguous, deterministic summation order."""
+    ldh, ldg = _ld(H, "H"), _ld(G, "G")
+    if H.size(0) != G.size(0):
+        raise RuntimeError("cagnet_b200: gemm_tn row mismatch")
+    n, K, N = H.size(0), H.size(1), G.size(1)
+    out = torch.empty((K, N), dtype=torch.float32, device=H.device)
+    nbytes = _native.lib().cagnet_gemm_tn_workspace_bytes(n, K, N)
+    ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=H.device)
+    with torch.cuda.device(H.device):
+        _native.check(_native.lib().cagnet_gemm_tn_f32(H.data_ptr(), ldh, G.data_ptr(), ldg, out.data_ptr(), max(N, 1),
+                                                       n, K, N, ws.data_ptr(), ws.numel(), _stream()), "gemm_tn")
+    return out
+
+
+def relu(z):
+    out = empty_padded(z.size(0), z.size(1), z.device)
+    with torch.cuda.device(z.device):
+        _native.check(_native.lib().cagnet_relu_fwd_f32(z.data_ptr(), _ld(z, "z"), out.data_ptr(), _ld(out, "out"),
+                                                        z.size(0), z.size(1), _stream()), "relu_fwd")
+    return out
+
+
+def relu_bwd(h, g):
+    out = empty_padded(h.size(0), h.size(1), h.device)
+    with torch.cuda.device(h.device):
+        _native.check(_native.lib().cagnet_relu_bwd_f32(h.data_ptr(), _ld(h, "h"), g.data_ptr(), _ld(g, "g"),
+                                                        out.data_ptr(), _ld(out, "out"), h.size(0), h.size(1),
+                                                        _stream()), "relu_bwd")
+    return out
+
+
+def log_softmax(z):
+    out = empty_padded(z.size(0), z.size(1), z.device)
+    with torch.cuda.device(z.device):
+        _native.check(_native.lib().cagnet_log_softmax_fwd_f32(z.data_ptr(), _ld(z, "z"), out.data_ptr(),
+                                                               _ld(out, "out"), z.size(0), z.size(1), _stream()),
+                      "log_softmax_fwd")
+    return out
+
+
+def log_softmax_bwd(logp, g):
+    out = empty_padded(logp.size(0), logp.size(1), logp.device)
+    with torch.cuda.device(logp.device):
+        _native.check(_native.lib().cagnet_log_softmax_bwd_f32(logp.data_ptr(), _ld(logp, "logp"), g.data_ptr(),
+                                                               _ld(g, "g"), out.data_ptr(), _ld(out, "out"),
+                                                               logp.size(0), logp.size(1), _stream()),
+                      "log_softmax_bwd")
+    return out
+
+
+def nll_masked(logp, y, mask, count, cls_lo=0, cls_hi=None, scale=1.0, want_grad=True):
+    """(loss, grad): loss = -sum_{mask} logp[i, y_i - cls_lo] / count over rows whose label is in
+    [cls_lo, cls_hi); grad = d(scale * loss)/d logp as a dense padded matrix (or None)."""
+    n, N = logp.shape
+    cls_hi = cls_lo + N if cls_hi is None else cls_hi
+    if y.dtype != torch.int64 or not y.is_cuda or mask.dtype not in (torch.bool, torch.uint8) or not mask.is_cuda:
+        raise RuntimeError("cagnet_b200: nll_masked needs int64 labels and a bool/uint8 mask on the device")
+    y = y.contiguous()
+    mask_u8 = mask.contiguous().view(torch.uint8)
+    loss = torch.empty((), dtype=torch.float32, device=logp.device)
+    grad = empty_padded(n, N, logp.device) if want_grad else None
+    nbytes = _native.lib().cagnet_nll_workspace_bytes(n)
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=logp.device)
+    with torch.cuda.device(logp.device):
+        _native.check(_native.lib().cagnet_nll_masked_f32(
+            logp.data_ptr(), _ld(logp, "logp"), y.data_ptr(), mask_u8.data_ptr(), n, N, int(cls_lo), int(cls_hi),
+            float(count), float(scale), loss.data_ptr(), None if grad is None else grad.data_ptr(),
+            0 if grad is None else _ld(grad, "grad"), ws.data_ptr(), ws.numel(), _stream()), "nll_masked")
+    return loss, grad

@@ -1,0 +1,123 @@
+/*
+ * cagnet_b200 -- C ABI of the B200 (sm_100a) kernels behind CAGNET's full-batch GCN hot path.
+ *
+ * Plain pointers and sizes only: every pointer is a DEVICE pointer unless its comment says host,
+ * every matrix is fp32 row-major with an explicit leading dimension (elements, not bytes), sparse
+ * indices are int32, `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream).
+ * Nothing here allocates, frees or synchronises unless its comment says so: scratch memory is
+ * passed in by the caller.  Every function returns 0 on success or one of the CAGNET_E_* codes;
+ * cagnet_last_error_string() describes the last failure on the calling thread.
+ *
+ * The reference interface each entry point replaces is cited as file:line of PASSIONLab/CAGNET.
+ */
+#ifndef CAGNET_B200_H
+#define CAGNET_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  CAGNET_OK = 0,
+  CAGNET_E_ARG = 1,        /* null pointer, negative size, bad enum */
+  CAGNET_E_ALIGN = 2,      /* leading dimension smaller than the width, or a misaligned pointer */
+  CAGNET_E_OVERFLOW = 3,   /* a size does not fit the 32-bit index type of the kernels */
+  CAGNET_E_LAUNCH = 4,     /* CUDA reported an error at launch */
+  CAGNET_E_WORKSPACE = 5,  /* scratch buffer too small */
+  CAGNET_E_INVALID = 6     /* device-side validation found malformed input */
+};
+
+/* Epilogues of cagnet_gemm_nn_f32. */
+enum {
+  CAGNET_EPI_NONE = 0,
+  CAGNET_EPI_RELU = 1,         /* out = max(acc, 0)                         F.relu,        gcn_distr.py:287-288 */
+  CAGNET_EPI_LOG_SOFTMAX = 2,  /* out = log_softmax(acc) per row (N <= 64)  F.log_softmax, gcn_distr.py:285-286 */
+  CAGNET_EPI_RELU_MASK = 3     /* out = aux > 0 ? acc : 0  (ReLU backward;  replaces autograd.grad at gcn_distr.py:312-322) */
+};
+
+int cagnet_version(void);
+const char* cagnet_last_error_string(void);
+
+/* Tuning knobs, for sweeps: "spmm_nv" (vectors per lane, 0 = automatic), "spmm_long" (rows with
+ * more nonzeros than this are processed by a whole thread block; must match between plan and
+ * multiply).  Host-side global state; returns CAGNET_E_ARG for an unknown name. */
+int cagnet_set_param(const char* name, int value);
+int cagnet_get_param(const char* name);
+
+/* ---- COO row indices -> CSR row offsets: rowptr[i] = |{e : rows[e] < i}|, i in [0, n].
+ * `rows` sorted ascending (a coalesced COO).  Bit-exact integer work.
+ * Replaces cusparseXcoo2csr at sparse-extension/sparse_coo_tensor.cu:137-142. */
+int cagnet_coo2csr_i32(const int32_t* rows, int64_t nnz, int32_t n, int32_t* rowptr, void* stream);
+
+/* Device-side validation of a CSR block: rowptr monotone, rowptr[0]=0, rowptr[n]=nnz, columns in
+ * [0, m).  Writes 0 (valid) or a non-zero reason code to *status_dev (one int32 on the device);
+ * the caller reads it back.  No counterpart in the reference, which never validates
+ * (sparse_coo_tensor.cu:43-54 skips even torch's checks). */
+int cagnet_check_csr_i32(const int32_t* rowptr, const int32_t* col, int32_t n, int32_t m, int64_t nnz,
+                         int32_t* status_dev, void* stream);
+
+/* ---- SpMM plan: lists the rows of a CSR block that are long enough to need a whole thread block.
+ * Scratch layout is opaque; size it with cagnet_spmm_plan_bytes(n, nnz).  Build once per block
+ * (the adjacency never changes), reuse for every multiply.  */
+size_t cagnet_spmm_plan_bytes(int32_t n, int64_t nnz);
+int cagnet_spmm_plan_i32(const int32_t* rowptr, int32_t n, int64_t nnz, void* plan, size_t plan_bytes, void* stream);
+
+/* ---- C = beta*C + A*B.  A: n x m CSR (rowptr[n+1], col[nnz], val[nnz]); B: m x f, ldb; C: n x f, ldc.
+ * beta is 0 (overwrite) or 1 (accumulate, the reference's in-place `C += A.B`).
+ * `plan` may be NULL (every row is then processed by one warp).  If ldb and ldc are multiples of 4
+ * (2) and B, C are 16-byte (8-byte) aligned the kernel moves 128-bit (64-bit) vectors; columns
+ * [f, ld) of such padded rows may be read and overwritten with unspecified values.
+ * Replaces cusparseSpMM(alpha=1, beta=1, CSRMM_ALG1) plus the row/column-major re-layouts around
+ * it at sparse-extension/sparse_coo_tensor.cu:149-226. */
+int cagnet_spmm_csr_f32(const int32_t* rowptr, const int32_t* col, const float* val,
+                        int32_t n, int32_t m, int64_t nnz,
+                        const float* B, int64_t ldb, float* C, int64_t ldc, int32_t f, float beta,
+                        const void* plan, void* stream);
+
+/* ---- Z = epilogue(X * W) for a tall X (n x K, ldx) and a small W.
+ * transW = 0: W is K x N row-major (ldw);  transW = 1: W is N x K row-major (ldw) and is used
+ * transposed (the `mm(ag, weight.t())` form).  aux (n x N, ldaux) is read by CAGNET_EPI_RELU_MASK only.
+ * Replaces torch.mm at gcn_distr.py:275 and :330 and the activations at gcn_distr.py:284-294. */
+int cagnet_gemm_nn_f32(const float* X, int64_t ldx, const float* W, int64_t ldw, int32_t transW,
+                       float* Z, int64_t ldz, int64_t n, int32_t K, int32_t N,
+                       int32_t epilogue, const float* aux, int64_t ldaux, void* stream);
+
+/* ---- out (K x N, ldo) = H^T * G for tall H (n x K, ldh) and G (n x N, ldg): the weight gradient.
+ * Split over row chunks, partial products in `ws`, summed in chunk order (deterministic).
+ * Size ws with cagnet_gemm_tn_workspace_bytes.  Replaces torch.mm(inputs.t(), ag) at
+ * gcn_distr.py:187 (outer_product2). */
+size_t cagnet_gemm_tn_workspace_bytes(int64_t n, int32_t K, int32_t N);
+int cagnet_gemm_tn_f32(const float* H, int64_t ldh, const float* G, int64_t ldg,
+                       float* out, int64_t ldo, int64_t n, int32_t K, int32_t N,
+                       void* ws, size_t ws_bytes, void* stream);
+
+/* ---- Elementwise / row-wise pieces, for callers that do not use the fused epilogues. */
+int cagnet_relu_fwd_f32(const float* z, int64_t ldz, float* h, int64_t ldh, int64_t n, int32_t N, void* stream);
+/* dz = h > 0 ? g : 0 */
+int cagnet_relu_bwd_f32(const float* h, int64_t ldh, const float* g, int64_t ldg, float* dz, int64_t lddz,
+                        int64_t n, int32_t N, void* stream);
+int cagnet_log_softmax_fwd_f32(const float* z, int64_t ldz, float* logp, int64_t ldl, int64_t n, int32_t N, void* stream);
+/* dz = g - exp(logp) * rowsum(g): the closed form of what gcn_distr.py:312-322 obtains by re-running
+ * log_softmax under autograd. */
+int cagnet_log_softmax_bwd_f32(const float* logp, int64_t ldl, const float* g, int64_t ldg, float* dz, int64_t lddz,
+                               int64_t n, int32_t N, void* stream);
+
+/* ---- Masked NLL: loss = -(1/count) * sum_{i: mask[i]} logp[i, y[i]];  writes the scalar to
+ * *loss_dev and, if grad != NULL, grad[i, j] = -scale/count at (i, y[i]) for masked rows, else 0
+ * (all n x N entries are written).  Rows whose label lies outside [cls_lo, cls_hi) are skipped
+ * (the class-column restriction of the 2D/3D loss, gcn_distr_2d.py:962-989); labels are rebased
+ * by cls_lo.  count is supplied by the caller (number of rows the mean runs over).
+ * ws: cagnet_nll_workspace_bytes(n).  Replaces F.nll_loss(outputs[mask], y[mask]) at
+ * gcn_distr.py:356 and its autograd backward. */
+size_t cagnet_nll_workspace_bytes(int64_t n);
+int cagnet_nll_masked_f32(const float* logp, int64_t ldl, const int64_t* y, const uint8_t* mask,
+                          int64_t n, int32_t N, int32_t cls_lo, int32_t cls_hi, float count, float scale,
+                          float* loss_dev, float* grad, int64_t ldg, void* ws, size_t ws_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CAGNET_B200_H */
