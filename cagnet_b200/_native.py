@@ -18,13 +18,16 @@ PROTOTYPES = {
     "cagnet_set_param": (_i32, [_cp, _i32]),
     "cagnet_get_param": (_i32, [_cp]),
     "cagnet_coo2csr_i32": (_i32, [_vp, _i64, _i32, _vp, _vp]),
-    "cagnet_check_csr_i32": (_i32, [_vp, _vp, _i32, _i32, _i64, _vp, _vp]),
+    "cagnet_check_csr_i32": (_i32, [_vp, _vp, _vp, _i32, _i32, _i64, _vp, _vp]),
     "cagnet_spmm_plan_bytes": (_sz, [_i32, _i64]),
     "cagnet_spmm_plan_i32": (_i32, [_vp, _i32, _i64, _vp, _sz, _vp]),
     "cagnet_spmm_csr_f32": (_i32, [_vp, _vp, _vp, _i32, _i32, _i64, _vp, _i64, _vp, _i64, _i32, _f32, _vp, _vp]),
     "cagnet_gemm_nn_f32": (_i32, [_vp, _i64, _vp, _i64, _i32, _vp, _i64, _i64, _i32, _i32, _i32, _vp, _i64, _vp]),
     "cagnet_gemm_tn_workspace_bytes": (_sz, [_i64, _i32, _i32]),
-    "cagnet_gemm_tn_f32": (_i32, [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _i32, _i32, _vp, _sz, _vp]),
+    "cagnet_gemm_tn_f32": (_i32, [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _i32, _i32, _f32, _vp, _sz, _vp]),
+    "cagnet_row_reduce_f32": (_i32, [_vp, _i64, _i64, _i32, _i32, _vp, _vp, _vp]),
+    "cagnet_log_softmax_apply_f32": (_i32, [_vp, _i64, _vp, _vp, _vp, _i64, _i64, _i32, _vp]),
+    "cagnet_log_softmax_bwd_apply_f32": (_i32, [_vp, _i64, _vp, _i64, _vp, _vp, _i64, _i64, _i32, _vp]),
     "cagnet_relu_fwd_f32": (_i32, [_vp, _i64, _vp, _i64, _i64, _i32, _vp]),
     "cagnet_relu_bwd_f32": (_i32, [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _i32, _vp]),
     "cagnet_log_softmax_fwd_f32": (_i32, [_vp, _i64, _vp, _i64, _i64, _i32, _vp]),

@@ -114,6 +114,7 @@ __global__ void __launch_bounds__(256) gemm_nn_kernel(const float* __restrict__ 
         float v = acc[i][t];
         if (epilogue == CAGNET_EPI_RELU) v = fmaxf(v, 0.f);
         else if (epilogue == CAGNET_EPI_RELU_MASK) v = (__ldg(aux + gr * ldaux + c) > 0.f) ? v : 0.f;
+        else if (epilogue == CAGNET_EPI_ACCUMULATE) v += Z[gr * ldz + c];
         Z[gr * ldz + c] = v;
       }
     }
@@ -194,12 +195,13 @@ __global__ void __launch_bounds__(256) gemm_tn_partial_kernel(const float* __res
 }
 
 __global__ void gemm_tn_reduce_kernel(const float* __restrict__ ws, int chunks, int K, int N, float* __restrict__ out,
-                                      int64_t ldo) {
+                                      int64_t ldo, float beta) {
   const int idx = blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= K * N) return;
   float s = 0.f;
   for (int c = 0; c < chunks; ++c) s += ws[static_cast<int64_t>(c) * K * N + idx];  // fixed order
-  out[static_cast<int64_t>(idx / N) * ldo + idx % N] = s;
+  float* o = out + static_cast<int64_t>(idx / N) * ldo + idx % N;
+  *o = (beta != 0.f) ? s + *o : s;
 }
 
 struct TnShape {
@@ -280,6 +282,46 @@ __global__ void log_softmax_bwd_kernel(const float* __restrict__ logp, int64_t l
   for (int c = lane; c < N; c += 32) dz[row * lddz + c] = g[row * ldg + c] - expf(logp[row * ldl + c]) * sum;
 }
 
+// Pieces of a log-softmax whose rows are split over several processes: every process reduces its own
+// columns, the per-row scalars are combined by a collective, then applied.   mode: 0 max, 1 sum,
+// 2 sum of exp(z - ref[row]).  One warp per row.
+__global__ void row_reduce_kernel(const float* __restrict__ z, int64_t ldz, int64_t n, int N, int mode,
+                                  const float* __restrict__ ref, float* __restrict__ out) {
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= n) return;
+  const int lane = threadIdx.x & 31;
+  const float* zp = z + row * ldz;
+  float acc = (mode == 0) ? -INFINITY : 0.f;
+  const float r = (mode == 2) ? ref[row] : 0.f;
+  for (int c = lane; c < N; c += 32) {
+    const float v = zp[c];
+    if (mode == 0) acc = fmaxf(acc, v);
+    else if (mode == 1) acc += v;
+    else acc += expf(v - r);
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    const float o = __shfl_xor_sync(0xffffffffu, acc, off);
+    acc = (mode == 0) ? fmaxf(acc, o) : acc + o;
+  }
+  if (lane == 0) out[row] = acc;
+}
+
+// mode 0: out = z - a[row] - log(b[row])        (log-softmax from the global row max a and sum b)
+// mode 1: out = g - exp(z) * a[row]             (its backward from log-probabilities z and the global row sum a of g)
+__global__ void row_apply_kernel(const float* __restrict__ z, int64_t ldz, const float* __restrict__ g, int64_t ldg,
+                                 const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ out,
+                                 int64_t ldo, int64_t n, int N, int mode) {
+  const int64_t total = n * N;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t r = i / N;
+    const int c = static_cast<int>(i - r * N);
+    if (mode == 0) out[r * ldo + c] = z[r * ldz + c] - a[r] - logf(b[r]);
+    else out[r * ldo + c] = g[r * ldg + c] - expf(z[r * ldz + c]) * a[r];
+  }
+}
+
 // ------------------------------------------------------------------------------------------------
 constexpr int kNllBlocks = 1024;
 
@@ -338,7 +380,7 @@ extern "C" int cagnet_gemm_nn_f32(const float* X, int64_t ldx, const float* W, i
   if (n < 0 || K < 0 || N < 0) return fail(CAGNET_E_ARG, "cagnet_gemm_nn_f32: negative size");
   if (n == 0 || N == 0) return CAGNET_OK;
   if (!X || !W || !Z) return fail(CAGNET_E_ARG, "cagnet_gemm_nn_f32: null pointer");
-  if (epilogue < 0 || epilogue > 3) return fail(CAGNET_E_ARG, "cagnet_gemm_nn_f32: unknown epilogue");
+  if (epilogue < 0 || epilogue > 4) return fail(CAGNET_E_ARG, "cagnet_gemm_nn_f32: unknown epilogue");
   if (epilogue == CAGNET_EPI_RELU_MASK && (!aux || ldaux < N))
     return fail(CAGNET_E_ARG, "cagnet_gemm_nn_f32: the ReLU-mask epilogue needs aux (n x N)");
   if (epilogue == CAGNET_EPI_LOG_SOFTMAX && N > 64)
@@ -370,9 +412,10 @@ extern "C" size_t cagnet_gemm_tn_workspace_bytes(int64_t n, int32_t K, int32_t N
 }
 
 extern "C" int cagnet_gemm_tn_f32(const float* H, int64_t ldh, const float* G, int64_t ldg, float* out, int64_t ldo,
-                                  int64_t n, int32_t K, int32_t N, void* ws, size_t ws_bytes, void* stream) {
+                                  int64_t n, int32_t K, int32_t N, float beta, void* ws, size_t ws_bytes, void* stream) {
   if (n < 0 || K < 0 || N < 0) return fail(CAGNET_E_ARG, "cagnet_gemm_tn_f32: negative size");
   if (K == 0 || N == 0) return CAGNET_OK;
+  if (beta != 0.f && beta != 1.f) return fail(CAGNET_E_ARG, "cagnet_gemm_tn_f32: beta must be 0 or 1");
   if (!out || !ws || (n > 0 && (!H || !G))) return fail(CAGNET_E_ARG, "cagnet_gemm_tn_f32: null pointer");
   if (ldh < K || ldg < N || ldo < N) return fail(CAGNET_E_ALIGN, "cagnet_gemm_tn_f32: leading dimension too small");
   if (static_cast<int64_t>(K) * N > INT_MAX) return fail(CAGNET_E_OVERFLOW, "cagnet_gemm_tn_f32: K*N exceeds int32");
@@ -383,7 +426,7 @@ extern "C" int cagnet_gemm_tn_f32(const float* H, int64_t ldh, const float* G, i
   const TnShape sh = tn_shape(n, K, N);
   gemm_tn_partial_kernel<<<dim3(sh.chunks, sh.ktiles, sh.ntiles), 256, 0, s>>>(H, ldh, G, ldg, n, K, N, sh.rows_per_chunk,
                                                                               static_cast<float*>(ws));
-  gemm_tn_reduce_kernel<<<(K * N + 255) / 256, 256, 0, s>>>(static_cast<const float*>(ws), sh.chunks, K, N, out, ldo);
+  gemm_tn_reduce_kernel<<<(K * N + 255) / 256, 256, 0, s>>>(static_cast<const float*>(ws), sh.chunks, K, N, out, ldo, beta);
   return check_launch("cagnet_gemm_tn_f32");
 }
 
@@ -426,6 +469,41 @@ extern "C" int cagnet_log_softmax_bwd_f32(const float* logp, int64_t ldl, const 
   log_softmax_bwd_kernel<<<static_cast<unsigned>((n + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       logp, ldl, g, ldg, dz, lddz, n, N);
   return check_launch("cagnet_log_softmax_bwd_f32");
+}
+
+extern "C" int cagnet_row_reduce_f32(const float* z, int64_t ldz, int64_t n, int32_t N, int32_t mode, const float* ref,
+                                     float* out, void* stream) {
+  if (n < 0 || N < 0) return fail(CAGNET_E_ARG, "cagnet_row_reduce_f32: negative size");
+  if (n == 0) return CAGNET_OK;
+  if (mode < 0 || mode > 2 || !out || (N > 0 && !z) || (mode == 2 && !ref) || ldz < N)
+    return fail(CAGNET_E_ARG, "cagnet_row_reduce_f32: bad argument");
+  if ((n + 7) / 8 > INT_MAX) return fail(CAGNET_E_OVERFLOW, "cagnet_row_reduce_f32: too many rows");
+  row_reduce_kernel<<<static_cast<unsigned>((n + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(z, ldz, n, N, mode,
+                                                                                                     ref, out);
+  return check_launch("cagnet_row_reduce_f32");
+}
+
+extern "C" int cagnet_log_softmax_apply_f32(const float* z, int64_t ldz, const float* row_max, const float* row_sum,
+                                            float* logp, int64_t ldl, int64_t n, int32_t N, void* stream) {
+  if (n < 0 || N < 0) return fail(CAGNET_E_ARG, "cagnet_log_softmax_apply_f32: negative size");
+  if (n == 0 || N == 0) return CAGNET_OK;
+  if (!z || !row_max || !row_sum || !logp || ldz < N || ldl < N)
+    return fail(CAGNET_E_ARG, "cagnet_log_softmax_apply_f32: bad argument");
+  row_apply_kernel<<<elementwise_blocks(n * N), 256, 0, static_cast<cudaStream_t>(stream)>>>(z, ldz, nullptr, 0, row_max,
+                                                                                           row_sum, logp, ldl, n, N, 0);
+  return check_launch("cagnet_log_softmax_apply_f32");
+}
+
+extern "C" int cagnet_log_softmax_bwd_apply_f32(const float* logp, int64_t ldl, const float* g, int64_t ldg,
+                                                const float* row_sum_g, float* dz, int64_t lddz, int64_t n, int32_t N,
+                                                void* stream) {
+  if (n < 0 || N < 0) return fail(CAGNET_E_ARG, "cagnet_log_softmax_bwd_apply_f32: negative size");
+  if (n == 0 || N == 0) return CAGNET_OK;
+  if (!logp || !g || !row_sum_g || !dz || ldl < N || ldg < N || lddz < N)
+    return fail(CAGNET_E_ARG, "cagnet_log_softmax_bwd_apply_f32: bad argument");
+  row_apply_kernel<<<elementwise_blocks(n * N), 256, 0, static_cast<cudaStream_t>(stream)>>>(logp, ldl, g, ldg, row_sum_g,
+                                                                                           nullptr, dz, lddz, n, N, 1);
+  return check_launch("cagnet_log_softmax_bwd_apply_f32");
 }
 
 extern "C" size_t cagnet_nll_workspace_bytes(int64_t n) {

@@ -33,9 +33,14 @@ __global__ void coo2csr_boundary_kernel(const int* __restrict__ rows, int nnz, i
   for (int r = prev + 1; r <= cur; ++r) rowptr[r] = static_cast<int>(e);
 }
 
-__global__ void check_csr_kernel(const int* __restrict__ rowptr, const int* __restrict__ col, int n, int m, int nnz,
-                                 int* status) {
+__global__ void check_csr_kernel(const int* __restrict__ rowptr, const int* __restrict__ col,
+                                 const int* __restrict__ rows, int n, int m, int nnz, int* status) {
   const int64_t t = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (rows && t < nnz) {
+    const int r = rows[t];
+    if (r < 0 || r >= n) atomicMax(status, 5);
+    else if (t > 0 && rows[t - 1] > r) atomicMax(status, 3);
+  }
   if (t == 0) {
     if (rowptr[0] != 0) atomicMax(status, 1);
     if (rowptr[n] != nnz) atomicMax(status, 2);
@@ -68,15 +73,15 @@ extern "C" int cagnet_coo2csr_i32(const int32_t* rows, int64_t nnz, int32_t n, i
   return check_launch("cagnet_coo2csr_i32");
 }
 
-extern "C" int cagnet_check_csr_i32(const int32_t* rowptr, const int32_t* col, int32_t n, int32_t m, int64_t nnz,
-                                    int32_t* status_dev, void* stream) {
+extern "C" int cagnet_check_csr_i32(const int32_t* rowptr, const int32_t* col, const int32_t* rows, int32_t n, int32_t m,
+                                    int64_t nnz, int32_t* status_dev, void* stream) {
   if (n < 0 || m < 0 || nnz < 0 || !rowptr || !status_dev || (nnz > 0 && !col))
     return fail(CAGNET_E_ARG, "cagnet_check_csr_i32: bad argument");
   if (nnz > INT_MAX) return fail(CAGNET_E_OVERFLOW, "cagnet_check_csr_i32: nnz %s%lld exceeds int32", "", nnz);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   cudaMemsetAsync(status_dev, 0, sizeof(int), s);
   const int64_t work = (nnz > n ? nnz : n) + 1;
-  check_csr_kernel<<<static_cast<unsigned>((work + 255) / 256), 256, 0, s>>>(rowptr, col, n, m, static_cast<int>(nnz),
-                                                                            status_dev);
+  check_csr_kernel<<<static_cast<unsigned>((work + 255) / 256), 256, 0, s>>>(rowptr, col, rows, n, m,
+                                                                            static_cast<int>(nnz), status_dev);
   return check_launch("cagnet_check_csr_i32");
 }

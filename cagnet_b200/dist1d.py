@@ -1,0 +1,342 @@
+"""1D (block-row) and 1.5D (block-row with replication factor c) full-batch GCN training.
+
+Host-side mirror of the reference's `gcn_distr.py` and `gcn_distr_15d.py`: same function names and
+argument meaning (`broad_func`, `GCNFunc`, `outer_product2`, `train`, `run`), same block schedule and
+collectives, same loss and update rule.  What differs is underneath: every local computation is a
+kernel of the native library on cached int32 CSR blocks, activations are fused into the dense product,
+the backward of the activation is closed-form, and the broadcast of block k+1 runs on NCCL's stream while
+block k is being multiplied.  With replication = 1 the 1.5D schedule IS the 1D one (P stages, source i
+at stage i), so one implementation serves both scripts.
+"""
+import math
+import statistics
+import time
+
+import torch
+import torch.distributed as dist
+import torch.nn.functional as F
+
+from . import partition
+from .backend import ACT_LOG_SOFTMAX, ACT_NONE, ACT_RELU
+from .timing import CATEGORIES_15D, CATEGORIES_1D, Timers
+
+
+class Data:
+    """Attribute bag with the two fields the training loop reads: `y` (int64 labels) and `train_mask`."""
+
+    def __init__(self, **kw):
+        self.__dict__.update(kw)
+
+    def to(self, device):
+        for k, v in list(self.__dict__.items()):
+            if torch.is_tensor(v):
+                self.__dict__[k] = v.to(device)
+        return self
+
+
+class Runtime:
+    """Per-process settings: what the reference keeps in module globals (gcn_distr.py:53-64)."""
+
+    def __init__(self, backend, activations=True, normalization=True, replication=1, timing=False, overlap=True,
+                 categories=None):
+        self.backend = backend
+        self.activations = bool(activations)
+        self.normalization = bool(normalization)
+        self.replication = int(replication)
+        self.overlap = bool(overlap)
+        cats = categories or (CATEGORIES_15D if replication > 1 else CATEGORIES_1D)
+        self.timers = Timers(cats, timing, getattr(backend, "synchronize", None))
+
+
+def act_name(func):
+    if func is F.relu or func == ACT_RELU:
+        return ACT_RELU
+    if func is F.log_softmax or func == ACT_LOG_SOFTMAX:
+        return ACT_LOG_SOFTMAX
+    return ACT_NONE
+
+
+def _group_size(group):
+    return dist.get_world_size(group) if dist.is_available() and dist.is_initialized() else 1
+
+
+# ------------------------------------------------------------------------------------------ schedule
+def broad_func(rt, node_count, am_partitions, inputs, rank, size, row_groups, col_groups, group):
+    """Z_r = sum over this rank's stages of A_blk[stage] . H_stage, then (1.5D) an all-reduce of Z_r over the
+    c replicas of the block row.  gcn_distr.py:203-246, gcn_distr_15d.py:173-245.
+
+    Each stage broadcasts one block of H inside the rank's column communicator and multiplies it by the
+    cached CSR block.  Two receive buffers alternate: the broadcast of stage k+1 is issued (async) before
+    the multiply of stage k is queued, so NCCL moves block k+1 while the SMs work on block k."""
+    be, c = rt.backend, rt.replication
+    inputs = be.as_matrix(inputs)
+    f = inputs.size(1)
+    stages = partition.stages_15d(rank, size, c)
+    rank_c, rank_col = rank // c, rank % c
+    col_group = col_groups[rank_col] if c > 1 else group
+    row_group = row_groups[rank_c] if c > 1 else None
+    comm = size > 1 and dist.is_initialized()
+    n_loc = be.block_shape(am_partitions[0])[0]
+    z = be.empty(n_loc, f)
+    if not stages:
+        be.wire(z).zero_()
+    max_rows = max(be.block_shape(b)[1] for b in am_partitions)
+    bufs = [None, None]
+
+    def post(i):
+        q, bid = stages[i]
+        rows = be.block_shape(am_partitions[bid])[1]
+        if q == rank:
+            tensor = inputs
+        else:
+            if bufs[i % 2] is None:
+                bufs[i % 2] = be.empty(max_rows, f)
+            tensor = bufs[i % 2][:rows]
+        rt.timers.count("bcast_words", rows * f)
+        work = dist.broadcast(be.wire(tensor), src=q, group=col_group, async_op=True) if comm else None
+        return tensor, work
+
+    serial = rt.timers.enabled or not rt.overlap
+    pending = None
+    for i, (q, bid) in enumerate(stages):
+        if serial:
+            with rt.timers.region("comm_time", "bcast_comm_time"):
+                tensor, work = post(i)
+                if work is not None:
+                    work.wait()
+        else:
+            tensor, work = pending if pending is not None else post(i)
+            pending = post(i + 1) if i + 1 < len(stages) else None
+            if work is not None:
+                work.wait()                      # stream-side wait: the host runs ahead
+        with rt.timers.region("comp_time", "scomp_time"):
+            be.spmm(am_partitions[bid], tensor, z, 0.0 if i == 0 else 1.0)
+    if c > 1 and comm:
+        with rt.timers.region("comm_time", "reduce_comm_time"):
+            dist.all_reduce(be.wire(z), op=dist.ReduceOp.SUM, group=row_group)
+    return z
+
+
+def outer_product2(rt, inputs, ag, rank, size, group):
+    """grad_W = H^T . (A G), summed over the block rows (gcn_distr.py:178-201)."""
+    be = rt.backend
+    with rt.timers.region("comp_time", "dcomp_time"):
+        grad_weight = be.mm_tn(be.as_matrix(inputs), ag)
+    if size > 1 and dist.is_initialized():
+        with rt.timers.region("comm_time", "op2_comm_time", "op_comm_time"):
+            dist.all_reduce(grad_weight, op=dist.ReduceOp.SUM, group=group)
+    return grad_weight
+
+
+class GCNFunc(torch.autograd.Function):
+    """One GCN layer: out = act((A . H) . W).  gcn_distr.py:248-339, gcn_distr_15d.py:247-345."""
+
+    @staticmethod
+    def forward(ctx, inputs, weight, adj_matrix, am_partitions, rank, size, group, row_groups, col_groups, func, rt):
+        be = rt.backend
+        act = act_name(func) if rt.activations else ACT_NONE
+        z = broad_func(rt, None, am_partitions, inputs, rank, size, row_groups, col_groups, group)
+        with rt.timers.region("comp_time", "dcomp_time"):
+            out = be.mm(z, weight.detach(), act)
+        ctx.save_for_backward(inputs, weight, out)
+        ctx.args = (am_partitions, rank, size, group, row_groups, col_groups, act, rt)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        inputs, weight, out = ctx.saved_tensors
+        am_partitions, rank, size, group, row_groups, col_groups, act, rt = ctx.args
+        be = rt.backend
+        # sigma'(Z) * G in closed form from the activation output (the reference re-runs the activation
+        # under autograd: gcn_distr.py:312-322)
+        dz = be.act_bwd(out, be.as_matrix(grad_output), act)
+        ag = broad_func(rt, None, am_partitions, dz, rank, size, row_groups, col_groups, group)
+        grad_input = None
+        if ctx.needs_input_grad[0]:
+            with rt.timers.region("comp_time", "dcomp_time"):
+                grad_input = be.mm_nt(ag, weight.detach())
+        reduce_group = col_groups[rank % rt.replication] if rt.replication > 1 else group
+        grad_weight = outer_product2(rt, inputs, ag, rank, size, reduce_group)
+        return grad_input, grad_weight, None, None, None, None, None, None, None, None, None
+
+
+class MaskedNLL(torch.autograd.Function):
+    """mean over the masked rows of -outputs[i, y_i] (F.nll_loss(outputs[mask], y[mask]), gcn_distr.py:356),
+    loss and gradient from one fused kernel."""
+
+    @staticmethod
+    def forward(ctx, outputs, y, mask, count, rt, cls_lo, cls_hi, denom):
+        loss, grad = rt.backend.nll(rt.backend.as_matrix(outputs), y, mask, denom, cls_lo, cls_hi)
+        ctx.grad = grad
+        ctx.wire = rt.backend.wire
+        return loss
+
+    @staticmethod
+    def backward(ctx, g):
+        grad = ctx.grad
+        ctx.wire(grad).mul_(g)
+        return grad, None, None, None, None, None, None, None
+
+
+class Model:
+    """What `run()` builds once per process: cached device blocks, this rank's features, labels and mask."""
+
+    def __init__(self, rt, rank, size, inputs, adj_matrix, data, features, classes, group=None, row_groups=None,
+                 col_groups=None):
+        be, c = rt.backend, rt.replication
+        self.rt, self.rank, self.size, self.features, self.classes = rt, rank, size, features, classes
+        self.group, self.row_groups, self.col_groups = group, row_groups, col_groups
+        node_count = inputs.size(0)
+        self.node_count = node_count
+        inputs_loc, blocks = partition.oned_partition(rank, size, inputs, adj_matrix, rt.normalization, c)
+        self.inputs_loc = be.as_matrix(inputs_loc)
+        self.am_pbyp = [be.make_block(b) for b in blocks]
+        n_per_proc = int(math.ceil(float(node_count) / (size / c)))
+        rank_c = rank // c
+        lo, hi = rank_c * n_per_proc, min(node_count, (rank_c + 1) * n_per_proc)
+        dev = self.inputs_loc.device
+        self.rank_train_mask = data.train_mask[lo:hi].bool().to(dev)
+        self.datay_rank = data.y[lo:hi].long().to(dev)
+        self.train_count = int(self.rank_train_mask.sum())
+
+    def init_weights(self, mid_layer):
+        """torch.manual_seed(0); rand on the CPU, then moved (gcn_distr.py:550-560)."""
+        torch.manual_seed(0)
+        dev = self.inputs_loc.device
+        w1 = torch.rand(self.features, mid_layer, requires_grad=True).to(dev)
+        w2 = torch.rand(mid_layer, self.classes, requires_grad=True).to(dev)
+        self.weight1 = torch.nn.Parameter(w1.detach())
+        self.weight2 = torch.nn.Parameter(w2.detach())
+        self.optimizer = torch.optim.Adam([self.weight1, self.weight2], lr=0.01)
+        return self.weight1, self.weight2
+
+    def train(self):
+        return train(self.inputs_loc, self.weight1, self.weight2, None, self.am_pbyp, self.optimizer, self,
+                     self.rank, self.size, self.group, self.row_groups, self.col_groups, self.rt)
+
+
+def train(inputs, weight1, weight2, adj_matrix, am_partitions, optimizer, model, rank, size, group, row_groups,
+          col_groups, rt):
+    """One epoch: two layers, the rank-local mean NLL over its own train rows, backward, Adam step.
+    gcn_distr.py:341-366.  `model` supplies this rank's label / mask slices and its train-row count."""
+    outputs = GCNFunc.apply(inputs, weight1, adj_matrix, am_partitions, rank, size, group, row_groups, col_groups,
+                            F.relu, rt)
+    outputs = GCNFunc.apply(outputs, weight2, adj_matrix, am_partitions, rank, size, group, row_groups, col_groups,
+                            F.log_softmax, rt)
+    optimizer.zero_grad()
+    if model.train_count > 0:
+        loss = MaskedNLL.apply(outputs, model.datay_rank, model.rank_train_mask, model.train_count, rt, 0, None,
+                               model.train_count)
+        loss.backward()
+        model.last_loss = loss.detach()
+    else:
+        # no train rows here: a zero gradient still has to flow so that this rank joins the collectives of
+        # the backward pass (the reference's "fake loss", gcn_distr.py:359-362)
+        outputs.backward(rt.backend.zeros(outputs.size(0), outputs.size(1)))
+        model.last_loss = torch.zeros((), device=outputs.device)
+    optimizer.step()
+    return outputs
+
+
+def make_groups(rank, size, replication):
+    """All-ranks group plus the 1.5D row / column communicators; every rank creates every group, in the
+    same order (gcn_distr.py:532, gcn_distr_15d.py:398-419)."""
+    if not dist.is_initialized() or size == 1:
+        return None, None, None
+    group = dist.new_group(list(range(size)))
+    if replication == 1:
+        return group, None, None
+    rows, cols = partition.proc_groups_15d(size, replication)
+    row_groups = [dist.new_group(r) for r in rows]
+    col_groups = [dist.new_group(c) for c in cols]
+    return group, row_groups, col_groups
+
+
+def run(rank, size, inputs, adj_matrix, data, features, classes, rt, epochs, mid_layer, run_count, accuracy=False,
+        printer=print):
+    """Partition, then `run_count` runs of: reseed weights, one untimed epoch, `epochs - 1` timed epochs; report
+    the median run by rank-0 wall time with its per-category breakdown.  gcn_distr.py:524-669."""
+    group, row_groups, col_groups = make_groups(rank, size, rt.replication)
+    if rank // rt.replication >= size // rt.replication:
+        return None
+    model = Model(rt, rank, size, inputs, adj_matrix, data, features, classes, group, row_groups, col_groups)
+    printer(f"rank: {rank} adj_matrix_loc.size: torch.Size([{model.node_count}, {model.inputs_loc.size(0)}])")
+    printer(f"rank: {rank} inputs.size: {tuple(inputs.size())}")
+    timers = rt.timers
+    outputs = None
+    comm = group is not None
+
+    def sync():
+        if hasattr(rt.backend, "synchronize"):
+            rt.backend.synchronize()
+
+    for i in range(run_count):
+        timers.start_run(i)
+        model.init_weights(mid_layer)
+        if comm:
+            dist.barrier(group)
+        with timers.paused():                       # the first epoch is not timed
+            outputs = model.train()
+        if comm:
+            dist.barrier(group)
+        sync()
+        tstart = time.time()
+        printer(f"Starting training... rank {rank} run {i}")
+        for epoch in range(1, epochs):
+            outputs = model.train()
+            printer("Epoch: {:03d}".format(epoch))
+        sync()
+        timers.runs[i]["total_time"] = time.time() - tstart
+
+    if comm:
+        dist.barrier(group)
+    totals = [timers.runs[i]["total_time"] for i in range(run_count)]
+    median_idx = totals.index(statistics.median_low(totals))
+    if comm:
+        idx = torch.tensor([median_idx], device=model.inputs_loc.device)
+        dist.broadcast(idx, src=0, group=group)
+        median_idx = int(idx.item())
+    if rank == 0:
+        printer(f"total_times_r0: {totals}")
+    printer(f"rank: {rank} median_run: {median_idx}")
+    timers.report(rank, median_idx, printer=printer)
+    printer(f"rank: {rank} {outputs}")
+
+    if accuracy:
+        gathered = gather_outputs(model, outputs)
+        accs = test(gathered, data)
+        printer("Epoch: {:03d}, Train: {:.4f}, Val: {:.4f}, Test: {:.4f}".format(900, accs[0], accs[1], accs[2]))
+    model.outputs = outputs
+    return model
+
+
+def gather_outputs(model, outputs):
+    """All block rows of the final activations on every rank (gcn_distr.py:641-659)."""
+    rt, size, rank = model.rt, model.size, model.rank
+    c = rt.replication
+    rows_of = size // c
+    n, classes = model.node_count, model.classes
+    n_per_proc = int(math.ceil(float(n) / (size / c)))
+    dense = outputs.detach().contiguous()
+    if model.group is None:
+        return dense
+    if dense.size(0) != n_per_proc:
+        pad = torch.zeros(n_per_proc - dense.size(0), classes, device=dense.device)
+        dense = torch.cat([dense, pad], dim=0)
+    parts = [torch.zeros_like(dense) for _ in range(rows_of)]
+    dist.all_gather(parts, dense, group=model.col_groups[rank % c] if c > 1 else model.group)
+    return torch.cat(parts, dim=0)[:n]
+
+
+def test(outputs, data):
+    """Train / validation / test accuracy from gathered activations (gcn_distr.py:368-379)."""
+    accs = []
+    for name in ("train_mask", "val_mask", "test_mask"):
+        mask = getattr(data, name, None)
+        if mask is None:
+            accs.append(0)
+            continue
+        mask = mask.bool().to(outputs.device)
+        pred = outputs[mask].max(1)[1]
+        accs.append(pred.eq(data.y.to(outputs.device)[mask]).sum().item() / max(int(mask.sum().item()), 1))
+    return accs

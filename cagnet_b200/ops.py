@@ -9,8 +9,15 @@ import torch
 
 from . import _native
 
-EPI_NONE, EPI_RELU, EPI_LOG_SOFTMAX, EPI_RELU_MASK = 0, 1, 2, 3
+EPI_NONE, EPI_RELU, EPI_LOG_SOFTMAX, EPI_RELU_MASK, EPI_ACCUMULATE = 0, 1, 2, 3, 4
 _INT32_MAX = 2 ** 31 - 1
+
+# kernels of the native library launched by this process (every wrapper below adds what it launches)
+LAUNCHES = [0]
+
+
+def launch_count():
+    return LAUNCHES[0]
 
 
 def _stream():
@@ -23,15 +30,23 @@ def pad_ld(f):
     return (f + 3) // 4 * 4 if f <= 64 else (f + 31) // 32 * 32
 
 
+def _alias(storage_of, offset, shape, stride):
+    """A tensor over existing storage that autograd does not treat as a view of anything."""
+    out = torch.empty(0, dtype=torch.float32, device=storage_of.device)
+    return out.set_(storage_of.untyped_storage(), offset, shape, stride)
+
+
 def empty_padded(n, f, device):
-    """n x f fp32 view with stride (pad_ld(f), 1); `.base_buffer()` of it is the contiguous n x ld buffer."""
-    buf = torch.empty((n, pad_ld(f)), dtype=torch.float32, device=device)
-    return buf[:, :f]
+    """n x f fp32 matrix with strides (pad_ld(f), 1) over a buffer of n * ld elements; pad columns unspecified."""
+    ld = pad_ld(f)
+    flat = torch.empty(max(n * ld, 1), dtype=torch.float32, device=device)
+    return _alias(flat, 0, (n, f), (ld, 1))
 
 
 def zeros_padded(n, f, device):
-    buf = torch.zeros((n, pad_ld(f)), dtype=torch.float32, device=device)
-    return buf[:, :f]
+    ld = pad_ld(f)
+    flat = torch.zeros(max(n * ld, 1), dtype=torch.float32, device=device)
+    return _alias(flat, 0, (n, f), (ld, 1))
 
 
 def to_padded(x):
@@ -41,16 +56,34 @@ def to_padded(x):
     return out
 
 
-def base_buffer(view):
-    """The contiguous n x ld buffer behind a padded view (what a collective must move), or the view
-    itself when it is already contiguous."""
-    if view.is_contiguous():
-        return view
-    base = view._base
-    if base is not None and base.dim() == 2 and base.is_contiguous() and base.size(0) == view.size(0) \
-            and base.data_ptr() == view.data_ptr() and base.size(1) == view.stride(0):
-        return base
-    raise RuntimeError("cagnet_b200: tensor is neither contiguous nor a padded view")
+def base_buffer(x):
+    """The contiguous n x ld buffer behind a padded matrix (what a collective must move, pad columns included),
+    or x itself when it is already contiguous."""
+    if x.is_contiguous():
+        return x
+    if x.dim() == 2 and x.stride(1) == 1 and x.stride(0) >= x.size(1):
+        n, ld = x.size(0), x.stride(0)
+        need = (x.storage_offset() + n * ld) * x.element_size()
+        if x.untyped_storage().nbytes() >= need:
+            return _alias(x, x.storage_offset(), (n, ld), (ld, 1))
+    raise RuntimeError("cagnet_b200: tensor is neither contiguous nor a padded row-major matrix")
+
+
+def is_padded(x):
+    """True if x is a device fp32 matrix already in the layout `empty_padded` produces."""
+    if not (x.is_cuda and x.dtype == torch.float32 and x.dim() == 2):
+        return False
+    if x.size(0) > 1 and x.stride(0) != pad_ld(x.size(1)):
+        return False
+    if x.size(1) > 1 and x.stride(1) != 1:
+        return False
+    if x.storage_offset() % pad_ld(x.size(1)) != 0:      # a column slice of a wider matrix is not a padded matrix
+        return False
+    try:
+        base_buffer(x)
+    except RuntimeError:
+        return False
+    return True
 
 
 def _ld(t, name):
@@ -82,6 +115,7 @@ def coo2csr(rows, n):
     with torch.cuda.device(rows.device):
         _native.check(_native.lib().cagnet_coo2csr_i32(rows.data_ptr(), rows.numel(), n, rowptr.data_ptr(), _stream()),
                       "coo2csr")
+    LAUNCHES[0] += 1
     return rowptr
 
 
@@ -107,20 +141,24 @@ class CsrBlock:
         rowptr = coo2csr(rows32, n)
         blk = CsrBlock(rowptr, col32, val, n, m)
         if validate:
-            blk.validate()
+            blk.validate(rows32)
         if plan:
             blk.build_plan()
         return blk
 
-    def validate(self):
+    def validate(self, rows=None):
+        """Device-side check of the block (and of the sorted COO row indices it came from); one readback."""
         status = torch.zeros(1, dtype=torch.int32, device=self.val.device)
         with torch.cuda.device(self.val.device):
-            _native.check(_native.lib().cagnet_check_csr_i32(self.rowptr.data_ptr(), self.col.data_ptr(), self.n, self.m,
+            _native.check(_native.lib().cagnet_check_csr_i32(self.rowptr.data_ptr(), self.col.data_ptr(),
+                                                             None if rows is None else rows.data_ptr(), self.n, self.m,
                                                              self.nnz, status.data_ptr(), _stream()), "check_csr")
+        LAUNCHES[0] += 1
         code = int(status.item())
         if code:
             reason = {1: "rowptr[0] != 0", 2: "rowptr[n] != nnz (row index out of range or unsorted)",
-                      3: "row indices not sorted", 4: "column index out of range"}.get(code, "?")
+                      3: "row indices not sorted", 4: "column index out of range",
+                      5: "row index out of range"}.get(code, "?")
             raise RuntimeError("cagnet_b200: malformed sparse block: " + reason)
 
     def build_plan(self):
@@ -130,6 +168,7 @@ class CsrBlock:
             _native.check(_native.lib().cagnet_spmm_plan_i32(self.rowptr.data_ptr(), self.n, self.nnz,
                                                              self.plan.data_ptr(), self.plan.numel(), _stream()),
                           "spmm_plan")
+        LAUNCHES[0] += 2
 
     def long_rows(self):
         """Number of rows the plan routes to the block-per-row kernel (synchronises)."""
@@ -154,6 +193,7 @@ def spmm(block, B, C, beta=1.0):
             block.rowptr.data_ptr(), block.col.data_ptr(), block.val.data_ptr(), block.n, block.m, block.nnz,
             B.data_ptr(), ldb, C.data_ptr(), ldc, B.size(1), float(beta),
             None if block.plan is None else block.plan.data_ptr(), _stream()), "spmm")
+    LAUNCHES[0] += 1 if block.plan is None else 2
     return C
 
 
@@ -203,21 +243,65 @@ def gemm_nn(X, W, trans_w=False, epilogue=EPI_NONE, aux=None, out=None):
         _native.check(_native.lib().cagnet_gemm_nn_f32(X.data_ptr(), ldx, W.data_ptr(), ldw, int(bool(trans_w)),
                                                        out.data_ptr(), ldz, X.size(0), K, N, int(epilogue), aux_ptr,
                                                        ldaux, _stream()), "gemm_nn")
+    LAUNCHES[0] += 1
     return out
 
 
-def gemm_tn(H, G):
-    """H.T @ G for tall H (n x K) and G (n x N): K x N contiguous, deterministic summation order."""
+def gemm_tn(H, G, out=None, accumulate=False):
+    """H.T @ G for tall H (n x K) and G (n x N): K x N, deterministic summation order.  With `out` and
+    accumulate=True the product is added to out in place."""
     ldh, ldg = _ld(H, "H"), _ld(G, "G")
     if H.size(0) != G.size(0):
         raise RuntimeError("cagnet_b200: gemm_tn row mismatch")
     n, K, N = H.size(0), H.size(1), G.size(1)
-    out = torch.empty((K, N), dtype=torch.float32, device=H.device)
+    if out is None:
+        if accumulate:
+            raise RuntimeError("cagnet_b200: gemm_tn accumulate needs an output matrix")
+        out = torch.empty((K, N), dtype=torch.float32, device=H.device)
+    elif tuple(out.shape) != (K, N):
+        raise RuntimeError("cagnet_b200: gemm_tn output shape mismatch")
+    ldo = _ld(out, "out")
     nbytes = _native.lib().cagnet_gemm_tn_workspace_bytes(n, K, N)
     ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=H.device)
     with torch.cuda.device(H.device):
-        _native.check(_native.lib().cagnet_gemm_tn_f32(H.data_ptr(), ldh, G.data_ptr(), ldg, out.data_ptr(), max(N, 1),
-                                                       n, K, N, ws.data_ptr(), ws.numel(), _stream()), "gemm_tn")
+        _native.check(_native.lib().cagnet_gemm_tn_f32(H.data_ptr(), ldh, G.data_ptr(), ldg, out.data_ptr(), ldo,
+                                                       n, K, N, 1.0 if accumulate else 0.0, ws.data_ptr(), ws.numel(),
+                                                       _stream()), "gemm_tn")
+    LAUNCHES[0] += 2
+    return out
+
+
+ROW_MAX, ROW_SUM, ROW_SUMEXP = 0, 1, 2
+
+
+def row_reduce(z, mode, ref=None):
+    """Per-row max / sum / sum of exp(z - ref) over the columns of z: fp32 vector of n entries."""
+    out = torch.empty(z.size(0), dtype=torch.float32, device=z.device)
+    with torch.cuda.device(z.device):
+        _native.check(_native.lib().cagnet_row_reduce_f32(z.data_ptr(), _ld(z, "z"), z.size(0), z.size(1), int(mode),
+                                                          None if ref is None else ref.data_ptr(), out.data_ptr(),
+                                                          _stream()), "row_reduce")
+    LAUNCHES[0] += 1
+    return out
+
+
+def log_softmax_apply(z, row_max, row_sum):
+    out = empty_padded(z.size(0), z.size(1), z.device)
+    with torch.cuda.device(z.device):
+        _native.check(_native.lib().cagnet_log_softmax_apply_f32(z.data_ptr(), _ld(z, "z"), row_max.data_ptr(),
+                                                                 row_sum.data_ptr(), out.data_ptr(), _ld(out, "out"),
+                                                                 z.size(0), z.size(1), _stream()), "log_softmax_apply")
+    LAUNCHES[0] += 1
+    return out
+
+
+def log_softmax_bwd_apply(logp, g, row_sum_g):
+    out = empty_padded(logp.size(0), logp.size(1), logp.device)
+    with torch.cuda.device(logp.device):
+        _native.check(_native.lib().cagnet_log_softmax_bwd_apply_f32(
+            logp.data_ptr(), _ld(logp, "logp"), g.data_ptr(), _ld(g, "g"), row_sum_g.data_ptr(), out.data_ptr(),
+            _ld(out, "out"), logp.size(0), logp.size(1), _stream()), "log_softmax_bwd_apply")
+    LAUNCHES[0] += 1
     return out
 
 
@@ -226,6 +310,7 @@ def relu(z):
     with torch.cuda.device(z.device):
         _native.check(_native.lib().cagnet_relu_fwd_f32(z.data_ptr(), _ld(z, "z"), out.data_ptr(), _ld(out, "out"),
                                                         z.size(0), z.size(1), _stream()), "relu_fwd")
+    LAUNCHES[0] += 1
     return out
 
 
@@ -235,6 +320,7 @@ def relu_bwd(h, g):
         _native.check(_native.lib().cagnet_relu_bwd_f32(h.data_ptr(), _ld(h, "h"), g.data_ptr(), _ld(g, "g"),
                                                         out.data_ptr(), _ld(out, "out"), h.size(0), h.size(1),
                                                         _stream()), "relu_bwd")
+    LAUNCHES[0] += 1
     return out
 
 
@@ -244,6 +330,7 @@ def log_softmax(z):
         _native.check(_native.lib().cagnet_log_softmax_fwd_f32(z.data_ptr(), _ld(z, "z"), out.data_ptr(),
                                                                _ld(out, "out"), z.size(0), z.size(1), _stream()),
                       "log_softmax_fwd")
+    LAUNCHES[0] += 1
     return out
 
 
@@ -254,6 +341,7 @@ def log_softmax_bwd(logp, g):
                                                                _ld(g, "g"), out.data_ptr(), _ld(out, "out"),
                                                                logp.size(0), logp.size(1), _stream()),
                       "log_softmax_bwd")
+    LAUNCHES[0] += 1
     return out
 
 
@@ -275,4 +363,5 @@ def nll_masked(logp, y, mask, count, cls_lo=0, cls_hi=None, scale=1.0, want_grad
             logp.data_ptr(), _ld(logp, "logp"), y.data_ptr(), mask_u8.data_ptr(), n, N, int(cls_lo), int(cls_hi),
             float(count), float(scale), loss.data_ptr(), None if grad is None else grad.data_ptr(),
             0 if grad is None else _ld(grad, "grad"), ws.data_ptr(), ws.numel(), _stream()), "nll_masked")
+    LAUNCHES[0] += 2
     return loss, grad

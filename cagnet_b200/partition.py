@@ -1,0 +1,179 @@
+"""Block partitioners, normalisation and communicator layouts of the four algorithms.
+
+Same results as the reference's CPU partitioners (`split_coo`, `scale_elements`, `oned_partition`,
+`twod_partition`, `threed_partition_loc`; gcn_distr.py:398-522, gcn_distr_2d.py:1032-1164,
+gcn_distr_3d.py:1163-1382) -- indices bit-exact, values bit-exact fp32 -- but computed with one range
+filter and one key sort per block instead of O(P) boolean scans of the whole edge list, in plain torch
+on whichever device holds the edge list (the GPU for the large graphs).
+"""
+import math
+from typing import NamedTuple
+
+import torch
+
+
+class Block(NamedTuple):
+    """Coalesced COO block, entries sorted by row then column."""
+    rows: torch.Tensor   # int64 [nnz]
+    cols: torch.Tensor   # int64 [nnz]
+    vals: torch.Tensor   # float32 [nnz]
+    n_rows: int
+    n_cols: int
+
+
+# ------------------------------------------------------------------------------------------ pieces
+def chunk_sizes(total, parts):
+    """Floor split, remainder on the last part (gcn_distr_2d.py:1136-1149)."""
+    per = total // parts
+    return [per] * (parts - 1) + [total - per * (parts - 1)]
+
+
+def boundaries(node_count, n_per_proc, keep=None):
+    """Block starts 0, n_per_proc, ... then node_count; 2D/3D keep only the first `keep` starts
+    (gcn_distr.py:399-400, gcn_distr_2d.py:1036-1038, gcn_distr_3d.py:1168-1170)."""
+    starts = list(range(0, node_count, n_per_proc))
+    if keep is not None:
+        starts = starts[:keep]
+    return starts + [node_count]
+
+
+def inv_sqrt_degree(adj, node_count):
+    """deg^-1/2 in fp64 then rounded to fp32, deg = occurrences as a row index in the whole edge list.
+    The reference takes `histc(rows, bins=n)` (gcn_distr.py:440), which equals this count whenever
+    vertices 0 and n-1 occur -- always the case once self loops are added."""
+    deg = torch.bincount(adj[0], minlength=node_count).double()
+    return deg.pow(-0.5).float()
+
+
+def coalesce_block(r, c, n_rows, n_cols, d_row=None, d_col=None):
+    """Entries (r, c) -> Block; duplicate entries add up (value = multiplicity) as `.coalesce()` does, then
+    val = d_row[r] * (val * d_col[c]): the two diagonal products of scale_elements (gcn_distr.py:458-464),
+    one fp32 rounding each."""
+    key, counts = torch.unique(r * n_cols + c, return_counts=True)
+    rows = torch.div(key, n_cols, rounding_mode="floor")
+    cols = key - rows * n_cols
+    vals = counts.to(torch.float32)
+    if d_row is not None:
+        vals = d_row[rows] * (vals * d_col[cols])
+    return Block(rows, cols, vals, int(n_rows), int(n_cols))
+
+
+def _in_range(x, lo, hi):
+    return (x >= lo) & (x < hi)
+
+
+# ------------------------------------------------------------------------------------------ 1D / 1.5D
+def oned_partition(rank, size, inputs, adj, normalization=True, replication=1):
+    """Blocks and feature rows of one rank for the 1D (replication = 1, gcn_distr.py:472-522) and 1.5D
+    (gcn_distr_15d.py:497-549) algorithms.  blocks[i] is what the layer multiplies by H_i: the
+    transpose of A[rows_i, cols_rank], coalesced (gcn_distr.py:546), n_rank x n_i."""
+    n = inputs.size(0)
+    n_per_proc = math.ceil(float(n) / (size / replication))
+    rank_c = rank // replication
+    vtx = boundaries(n, n_per_proc)
+    lo, hi = vtx[rank_c], vtx[rank_c + 1]
+    d = inv_sqrt_degree(adj, n) if normalization else None
+    sel = _in_range(adj[1], lo, hi)
+    u, v = adj[0][sel], adj[1][sel] - lo
+    blocks = []
+    for i in range(len(vtx) - 1):
+        s = _in_range(u, vtx[i], vtx[i + 1])
+        n_i = vtx[i + 1] - vtx[i]
+        # stored orientation: row = column vertex of A (local to this rank), column = row vertex (local to block i)
+        if normalization:
+            blocks.append(coalesce_block(v[s], u[s] - vtx[i], hi - lo, n_i, d[lo:hi], d[vtx[i]:vtx[i + 1]]))
+        else:
+            blocks.append(coalesce_block(v[s], u[s] - vtx[i], hi - lo, n_i))
+    inputs_loc = inputs[lo:hi]
+    return inputs_loc, blocks
+
+
+def proc_groups_15d(size, replication):
+    """Row groups [i, i + c), column groups range(i, P, c) (gcn_distr_15d.py:398-419)."""
+    rows = [list(range(i, i + replication)) for i in range(0, size, replication)]
+    cols = [list(range(i, size, replication)) for i in range(replication)]
+    return rows, cols
+
+
+def stages_15d(rank, size, replication):
+    """(source rank, block id) per stage for `rank` (gcn_distr_15d.py:194-208): replica column j walks blocks
+    j*(P/c^2) ..., the last replica also takes the remainder; with c = 1 this is the 1D loop."""
+    rank_col = rank % replication
+    per = size // (replication ** 2)
+    stages = per
+    if rank_col == replication - 1:
+        stages = (size // replication) - (replication - 1) * per
+    return [((rank_col * per + i) * replication + rank_col, rank_col * per + i) for i in range(stages)]
+
+
+# ------------------------------------------------------------------------------------------ 2D
+def grid_side_2d(size):
+    return math.floor(math.sqrt(size))
+
+
+def twod_partition(rank, size, inputs, adj, normalization=True, q=None):
+    """Block (rank_row, rank_col) of A -- not transposed -- and of H (rows and feature columns floor-split,
+    remainder last): gcn_distr_2d.py:1093-1164."""
+    n = inputs.size(0)
+    q = grid_side_2d(size) if q is None else q
+    rank_row, rank_col = rank // q, rank % q
+    vtx = boundaries(n, n // q, keep=q)
+    r0, r1, c0, c1 = vtx[rank_row], vtx[rank_row + 1], vtx[rank_col], vtx[rank_col + 1]
+    sel = _in_range(adj[0], r0, r1) & _in_range(adj[1], c0, c1)
+    u, v = adj[0][sel] - r0, adj[1][sel] - c0
+    if normalization:
+        d = inv_sqrt_degree(adj, n)
+        block = coalesce_block(u, v, r1 - r0, c1 - c0, d[r0:r1], d[c0:c1])
+    else:
+        block = coalesce_block(u, v, r1 - r0, c1 - c0)
+    fs = [0]
+    for w in chunk_sizes(inputs.size(1), q):
+        fs.append(fs[-1] + w)
+    inputs_loc = inputs[r0:r1, fs[rank_col]:fs[rank_col + 1]]
+    return inputs_loc, block
+
+
+def proc_groups_2d(size):
+    """gcn_distr_2d.py:516-535."""
+    q = grid_side_2d(size)
+    return [list(range(i * q, i * q + q)) for i in range(q)], [list(range(i, size, q)) for i in range(q)]
+
+
+# ------------------------------------------------------------------------------------------ 3D
+def grid_side_3d(size):
+    c = int(round(size ** (1.0 / 3.0)))
+    if c ** 3 != size:
+        raise ValueError("the 3D algorithm needs a cubic number of processes, got %d" % size)
+    return c
+
+
+def coords_3d(rank, q):
+    """rank = i*(q*c) + j*c + k with q = c (gcn_distr_3d.py:754-756)."""
+    return (rank // q) // q, (rank // q) % q, rank % q
+
+
+def threed_partition(rank, size, inputs, adj, normalization=False):
+    """2D block (i, j), then its columns cut into c slabs and the H block's rows into c chunks; this rank keeps
+    slab / chunk k (gcn_distr_3d.py:1533-1542, 1341-1382).  The reference never normalises here
+    (gcn_distr_3d.py:66); `normalization=True` is this package's extension and scales exactly as 2D does."""
+    q = grid_side_3d(size)
+    i, j, k = coords_3d(rank, q)
+    inputs_2d, blk = twod_partition(i * q + j, q * q, inputs, adj, normalization, q=q)
+    vtx = boundaries(blk.n_cols, blk.n_cols // q, keep=q)
+    s = _in_range(blk.cols, vtx[k], vtx[k + 1])
+    # the reference rebuilds the slab from the coalesced indices with unit values (gcn_distr_3d.py:1357-1364)
+    vals = blk.vals[s] if normalization else torch.ones_like(blk.vals[s])
+    slab = Block(blk.rows[s], blk.cols[s] - vtx[k], vals, blk.n_rows, vtx[k + 1] - vtx[k])
+    rs = [0]
+    for w in chunk_sizes(inputs_2d.size(0), q):
+        rs.append(rs[-1] + w)
+    return inputs_2d[rs[k]:rs[k + 1]], slab
+
+
+def proc_groups_3d(size):
+    """row_groups[i][k], col_groups[j][k], fiber groups [rank // c] (gcn_distr_3d.py:629-672)."""
+    q = grid_side_3d(size)
+    rows = [[list(range(i * q * q + k, (i + 1) * q * q + k, q)) for k in range(q)] for i in range(q)]
+    cols = [[list(range(j * q + k, q * q * q + j * q + k, q * q)) for k in range(q)] for j in range(q)]
+    fibers = [list(range(i, i + q)) for i in range(0, size, q)]
+    return rows, cols, fibers

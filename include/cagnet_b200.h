@@ -35,7 +35,8 @@ enum {
   CAGNET_EPI_NONE = 0,
   CAGNET_EPI_RELU = 1,         /* out = max(acc, 0)                         F.relu,        gcn_distr.py:287-288 */
   CAGNET_EPI_LOG_SOFTMAX = 2,  /* out = log_softmax(acc) per row (N <= 64)  F.log_softmax, gcn_distr.py:285-286 */
-  CAGNET_EPI_RELU_MASK = 3     /* out = aux > 0 ? acc : 0  (ReLU backward;  replaces autograd.grad at gcn_distr.py:312-322) */
+  CAGNET_EPI_RELU_MASK = 3,    /* out = aux > 0 ? acc : 0  (ReLU backward;  replaces autograd.grad at gcn_distr.py:312-322) */
+  CAGNET_EPI_ACCUMULATE = 4    /* out += acc               (`z_loc += torch.mm(acol, brow)`, gcn_distr_2d.py:507) */
 };
 
 int cagnet_version(void);
@@ -53,11 +54,13 @@ int cagnet_get_param(const char* name);
 int cagnet_coo2csr_i32(const int32_t* rows, int64_t nnz, int32_t n, int32_t* rowptr, void* stream);
 
 /* Device-side validation of a CSR block: rowptr monotone, rowptr[0]=0, rowptr[n]=nnz, columns in
- * [0, m).  Writes 0 (valid) or a non-zero reason code to *status_dev (one int32 on the device);
- * the caller reads it back.  No counterpart in the reference, which never validates
- * (sparse_coo_tensor.cu:43-54 skips even torch's checks). */
-int cagnet_check_csr_i32(const int32_t* rowptr, const int32_t* col, int32_t n, int32_t m, int64_t nnz,
-                         int32_t* status_dev, void* stream);
+ * [0, m) and, when the COO row indices the offsets were made from are passed (rows != NULL), rows in
+ * [0, n) and sorted ascending.  Writes 0 (valid) or a reason code (1 rowptr[0], 2 rowptr[n],
+ * 3 unsorted, 4 column range, 5 row range) to *status_dev (one int32 on the device); the caller
+ * reads it back.  No counterpart in the reference, which never validates (sparse_coo_tensor.cu:43-54
+ * skips even torch's checks). */
+int cagnet_check_csr_i32(const int32_t* rowptr, const int32_t* col, const int32_t* rows, int32_t n, int32_t m,
+                         int64_t nnz, int32_t* status_dev, void* stream);
 
 /* ---- SpMM plan: lists the rows of a CSR block that are long enough to need a whole thread block.
  * Scratch layout is opaque; size it with cagnet_spmm_plan_bytes(n, nnz).  Build once per block
@@ -85,13 +88,14 @@ int cagnet_gemm_nn_f32(const float* X, int64_t ldx, const float* W, int64_t ldw,
                        float* Z, int64_t ldz, int64_t n, int32_t K, int32_t N,
                        int32_t epilogue, const float* aux, int64_t ldaux, void* stream);
 
-/* ---- out (K x N, ldo) = H^T * G for tall H (n x K, ldh) and G (n x N, ldg): the weight gradient.
- * Split over row chunks, partial products in `ws`, summed in chunk order (deterministic).
- * Size ws with cagnet_gemm_tn_workspace_bytes.  Replaces torch.mm(inputs.t(), ag) at
- * gcn_distr.py:187 (outer_product2). */
+/* ---- out (K x N, ldo) = beta*out + H^T * G for tall H (n x K, ldh) and G (n x N, ldg): the weight
+ * gradient.  beta is 0 or 1.  Split over row chunks, partial products in `ws`, summed in chunk order
+ * (deterministic).  Size ws with cagnet_gemm_tn_workspace_bytes.  Replaces torch.mm(inputs.t(), ag) at
+ * gcn_distr.py:187 (outer_product2) and the accumulating `z_loc += torch.mm(acol, brow)` of the dense
+ * SUMMA at gcn_distr_2d.py:276 (whose left operand is a transposed block). */
 size_t cagnet_gemm_tn_workspace_bytes(int64_t n, int32_t K, int32_t N);
 int cagnet_gemm_tn_f32(const float* H, int64_t ldh, const float* G, int64_t ldg,
-                       float* out, int64_t ldo, int64_t n, int32_t K, int32_t N,
+                       float* out, int64_t ldo, int64_t n, int32_t K, int32_t N, float beta,
                        void* ws, size_t ws_bytes, void* stream);
 
 /* ---- Elementwise / row-wise pieces, for callers that do not use the fused epilogues. */
@@ -104,6 +108,21 @@ int cagnet_log_softmax_fwd_f32(const float* z, int64_t ldz, float* logp, int64_t
  * log_softmax under autograd. */
 int cagnet_log_softmax_bwd_f32(const float* logp, int64_t ldl, const float* g, int64_t ldg, float* dz, int64_t lddz,
                                int64_t n, int32_t N, void* stream);
+
+/* ---- Row-wise pieces of a log-softmax whose rows are split by columns over several processes
+ * (dist_log_softmax, gcn_distr_2d.py:537-568): each process reduces its own columns, the per-row scalars
+ * are combined by a collective between the calls.
+ * cagnet_row_reduce_f32: out[row] = max_c z (mode 0) | sum_c z (mode 1) | sum_c exp(z - ref[row]) (mode 2).
+ * cagnet_log_softmax_apply_f32: logp = z - row_max - log(row_sum).
+ * cagnet_log_softmax_bwd_apply_f32: dz = g - exp(logp) * row_sum_g (replaces the gather of full rows and
+ * the autograd call of dist_log_softmax2, gcn_distr_2d.py:570-645, 777-795). */
+int cagnet_row_reduce_f32(const float* z, int64_t ldz, int64_t n, int32_t N, int32_t mode, const float* ref,
+                          float* out, void* stream);
+int cagnet_log_softmax_apply_f32(const float* z, int64_t ldz, const float* row_max, const float* row_sum,
+                                 float* logp, int64_t ldl, int64_t n, int32_t N, void* stream);
+int cagnet_log_softmax_bwd_apply_f32(const float* logp, int64_t ldl, const float* g, int64_t ldg,
+                                     const float* row_sum_g, float* dz, int64_t lddz, int64_t n, int32_t N,
+                                     void* stream);
 
 /* ---- Masked NLL: loss = -(1/count) * sum_{i: mask[i]} logp[i, y[i]];  writes the scalar to
  * *loss_dev and, if grad != NULL, grad[i, j] = -scale/count at (i, y[i]) for masked rows, else 0

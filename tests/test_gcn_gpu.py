@@ -1,0 +1,87 @@
+"""Whole-epoch parity of the CUDA path (single GPU, P = 1): the reference's own fixture and the fp64 oracle."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import gcn as OG
+
+pytestmark = pytest.mark.gpu
+
+
+def _rel(a, b):
+    b = torch.as_tensor(b).double()
+    return float((torch.as_tensor(a).double().cpu() - b).abs().max() / max(float(b.abs().max()), 1e-30))
+
+
+def _model(x, adj, data, f, classes, activations=True, normalization=True):
+    from cagnet_b200 import dist1d
+    from cagnet_b200.backend import CudaBackend
+    rt = dist1d.Runtime(CudaBackend(), activations=activations, normalization=normalization)
+    return dist1d.Model(rt, 0, 1, x, adj, data, f, classes)
+
+
+@pytest.mark.parametrize("name", ["train_1d_P1.npz", "train_1d_P1_plain.npz"])
+def test_epochs_match_reference_fixture(golden_dir, name):
+    from cagnet_b200 import dist1d, graphs
+    d = np.load(os.path.join(golden_dir, name))
+    n, f, mid, classes, epochs, P, c, norm, act = d["cfg"].tolist()
+    edge, x, y, mask = (torch.from_numpy(d[k]) for k in ("edge_index", "x", "y", "mask"))
+    adj = graphs.add_self_loops(edge, n) if norm else edge
+    model = _model(x, adj, dist1d.Data(y=y, train_mask=mask), f, classes, bool(act), bool(norm))
+    model.init_weights(mid)
+    for ep in range(epochs):
+        out = model.train()
+        assert _rel(out.detach(), d[f"r0_ep{ep}_out"]) <= 1e-4
+        assert _rel(model.weight1.grad, d[f"r0_ep{ep}_gw1"]) <= 1e-4
+        assert _rel(model.weight2.grad, d[f"r0_ep{ep}_gw2"]) <= 1e-4
+        assert _rel(model.weight1.detach(), d[f"r0_ep{ep}_w1"]) <= 1e-4
+        assert _rel(model.weight2.detach(), d[f"r0_ep{ep}_w2"]) <= 1e-4
+
+
+def test_ten_epochs_on_the_cpu_runnable_config():
+    """The reference's CPU-runnable case: Erdos-Renyi 16,384 vertices, avg degree 16, 128 features, hidden 16,
+    8 classes, 10 epochs, ReLU, Adam lr 0.01.  Per-epoch loss and activations within 1e-4 of the fp64 oracle."""
+    from cagnet_b200 import datasets, graphs
+    x, edge, data, f, classes, _ = datasets.load("er:n=16384,deg=16,f=128,c=8", device="cpu")
+    n = x.size(0)
+    adj = graphs.add_self_loops(edge, n)
+    model = _model(x, adj, data, f, classes)
+    model.init_weights(16)
+    M = OG.matrix_1d(adj, x, 1, True, dtype=torch.float64)
+    rule = lambda y_, m_: (lambda out: OG.grad_local_mean(out, y_, m_, n))
+    ref = OG.train(M, x, data.y, data.train_mask, 16, classes, 10, rule, True, dtype=torch.float64)
+    for ep in range(10):
+        out = model.train()
+        assert _rel(out.detach(), ref[ep]["out"]) <= 1e-4, ep
+        assert abs(float(model.last_loss) - float(ref[ep]["loss"])) <= 1e-4 * abs(float(ref[ep]["loss"])), ep
+        assert _rel(model.weight1.detach(), ref[ep]["W1"]) <= 1e-4, ep
+
+
+def test_power_law_graph_epoch_and_linearity():
+    """R-MAT graph with hub rows: epoch parity, plus a size-independent property of the SpMM (linearity in B)."""
+    from cagnet_b200 import datasets, graphs, ops
+    x, edge, data, f, classes, _ = datasets.load("rmat:n=30000,nnz=3000000,f=602,c=41,train=0.66", device="cpu")
+    n = x.size(0)
+    adj = graphs.add_self_loops(edge, n)
+    model = _model(x, adj, data, f, classes)
+    model.init_weights(16)
+    M = OG.matrix_1d(adj, x, 1, True, dtype=torch.float64)
+    rule = lambda y_, m_: (lambda out: OG.grad_local_mean(out, y_, m_, n))
+    ref = OG.train(M, x, data.y, data.train_mask, 16, classes, 2, rule, True, dtype=torch.float64)
+    for ep in range(2):
+        out = model.train()
+        assert _rel(out.detach(), ref[ep]["out"]) <= 1e-4
+        assert _rel(model.weight1.grad, ref[ep]["gW1"]) <= 1e-4
+    A = model.am_pbyp[0]
+    b1, b2 = ops.to_padded(torch.randn(n, 41, device="cuda")), ops.to_padded(torch.randn(n, 41, device="cuda"))
+    c1, c2, c12 = (ops.zeros_padded(n, 41, "cuda") for _ in range(3))
+    ops.spmm(A, b1, c1, 0.0)
+    ops.spmm(A, b2, c2, 0.0)
+    ops.spmm(A, ops.to_padded(2 * b1 - b2), c12, 0.0)
+    assert _rel(c12, (2 * c1 - c2).cpu()) <= 1e-4
+    # a checksum that does not depend on the order of summation: 1^T (A B) == (1^T A) B
+    colsum = torch.zeros(n, dtype=torch.float64)
+    colsum.index_add_(0, A.col.cpu().long(), A.val.cpu().double())
+    assert _rel(c1.double().sum(0).cpu(), colsum @ b1.double().cpu()) <= 1e-4
