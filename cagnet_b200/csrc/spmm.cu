@@ -19,7 +19,8 @@
 namespace cagnet {
 
 struct Tuning {
-  int spmm_nv = 0;       // 0 = automatic
+  int spmm_tile = 0;     // vectors per feature tile: 0 = automatic, else 4, 8, 16, 32, 64, 96, 128 or 160
+  int spmm_rpb = 4;      // rows (warps) per thread block of the warp-per-row kernel: 1, 2, 4 or 8
   int spmm_long = 4096;  // rows with more nonzeros go to the block-per-row kernel
 };
 static Tuning g_tuning;
@@ -253,29 +254,41 @@ static int launch_spmm(const int* rowptr, const int* col, const float* val, int 
     spmm_block_rows_kernel<VEC, LPN, NV><<<dim3(blocks, tiles), kLongWarps * 32, 0, stream>>>(
         rowptr, col, val, B, ldb, C, ldc, f_eff, beta, plan);
   }
-  const int rows_per_block = 8;
+  const int rows_per_block = g_tuning.spmm_rpb;
   spmm_warp_rows_kernel<VEC, LPN, NV><<<dim3((n + rows_per_block - 1) / rows_per_block, tiles), rows_per_block * 32, 0,
                                         stream>>>(rowptr, col, val, n, B, ldb, C, ldc, f_eff, beta, plan);
   return check_launch("cagnet_spmm_csr_f32");
 }
 
+// Feature tiling.  A tile is `tile` vectors wide (tile * VEC columns); narrow B is covered by one tile of the
+// next power of two.  Wide B is cut into 32-vector tiles (128 columns with 128-bit vectors): measured on a
+// 233K-vertex / 115M-nonzero R-MAT graph at width 602, one 512-byte segment per gathered row and lane beat both
+// narrower tiles (more passes over the col/val streams, more shuffles per byte) and the full-width tile (fewer
+// resident warps, lower L1 hit rate on hub columns).
+static int auto_tile(int vectors) {
+  if (vectors <= 4) return 4;
+  if (vectors <= 8) return 8;
+  if (vectors <= 16) return 16;
+  return 32;
+}
+
 template <int VEC>
-static int dispatch_shape(int vectors, const int* rowptr, const int* col, const float* val, int n, int64_t nnz,
+static int dispatch_shape(int vectors, const int* rowptr, const int* col, const float* val, int n, int m, int64_t nnz,
                           const float* B, int64_t ldb, float* C, int64_t ldc, int f_eff, float beta, const int* plan,
                           cudaStream_t stream) {
 #define CAGNET_SPMM_CASE(LPN, NV) \
   return launch_spmm<VEC, LPN, NV>(rowptr, col, val, n, nnz, B, ldb, C, ldc, f_eff, beta, plan, stream)
-  if (vectors <= 4) CAGNET_SPMM_CASE(4, 1);
-  if (vectors <= 8) CAGNET_SPMM_CASE(8, 1);
-  if (vectors <= 16) CAGNET_SPMM_CASE(16, 1);
-  int nv = g_tuning.spmm_nv;
-  if (nv <= 0) nv = vectors <= 160 ? (vectors + 31) / 32 : 4;
-  nv = min(nv, (vectors + 31) / 32);
-  switch (nv) {
-    case 1: CAGNET_SPMM_CASE(32, 1);
-    case 2: CAGNET_SPMM_CASE(32, 2);
-    case 3: CAGNET_SPMM_CASE(32, 3);
-    case 4: CAGNET_SPMM_CASE(32, 4);
+  int tile = g_tuning.spmm_tile > 0 ? g_tuning.spmm_tile : auto_tile(vectors);
+  (void)m;
+  if (vectors <= 4) tile = 4;
+  switch (tile) {
+    case 4: CAGNET_SPMM_CASE(4, 1);
+    case 8: CAGNET_SPMM_CASE(8, 1);
+    case 16: CAGNET_SPMM_CASE(16, 1);
+    case 32: CAGNET_SPMM_CASE(32, 1);
+    case 64: CAGNET_SPMM_CASE(32, 2);
+    case 96: CAGNET_SPMM_CASE(32, 3);
+    case 128: CAGNET_SPMM_CASE(32, 4);
     default: CAGNET_SPMM_CASE(32, 5);
   }
 #undef CAGNET_SPMM_CASE
@@ -287,9 +300,19 @@ using namespace cagnet;
 
 extern "C" int cagnet_set_param(const char* name, int value) {
   if (!name) return fail(CAGNET_E_ARG, "cagnet_set_param: null name");
-  if (!strcmp(name, "spmm_nv")) {
-    if (value < 0 || value > 5) return fail(CAGNET_E_ARG, "cagnet_set_param: spmm_nv must be in [0, 5]");
-    g_tuning.spmm_nv = value;
+  if (!strcmp(name, "spmm_tile")) {
+    const int ok[] = {0, 4, 8, 16, 32, 64, 96, 128, 160};
+    for (int o : ok)
+      if (value == o) {
+        g_tuning.spmm_tile = value;
+        return CAGNET_OK;
+      }
+    return fail(CAGNET_E_ARG, "cagnet_set_param: spmm_tile must be 0, 4, 8, 16, 32, 64, 96, 128 or 160");
+  }
+  if (!strcmp(name, "spmm_rpb")) {
+    if (value != 1 && value != 2 && value != 4 && value != 8)
+      return fail(CAGNET_E_ARG, "cagnet_set_param: spmm_rpb must be 1, 2, 4 or 8");
+    g_tuning.spmm_rpb = value;
     return CAGNET_OK;
   }
   if (!strcmp(name, "spmm_long")) {
@@ -301,7 +324,8 @@ extern "C" int cagnet_set_param(const char* name, int value) {
 }
 
 extern "C" int cagnet_get_param(const char* name) {
-  if (name && !strcmp(name, "spmm_nv")) return g_tuning.spmm_nv;
+  if (name && !strcmp(name, "spmm_tile")) return g_tuning.spmm_tile;
+  if (name && !strcmp(name, "spmm_rpb")) return g_tuning.spmm_rpb;
   if (name && !strcmp(name, "spmm_long")) return g_tuning.spmm_long;
   return -1;
 }
@@ -345,11 +369,12 @@ extern "C" int cagnet_spmm_csr_f32(const int32_t* rowptr, const int32_t* col, co
   auto round_up = [](int x, int a) { return (x + a - 1) / a * a; };
   if (ldb % 4 == 0 && ldc % 4 == 0 && aligned(B, 16) && aligned(C, 16) && round_up(f, 4) <= ldb && round_up(f, 4) <= ldc) {
     const int f_eff = round_up(f, 4);
-    return dispatch_shape<4>(f_eff / 4, rowptr, col, val, n, nnz, B, ldb, C, ldc, f_eff, beta, p, s);
+    return dispatch_shape<4>(f_eff / 4, rowptr, col, val, n, m, nnz, B, ldb, C, ldc, f_eff, beta, p, s);
   }
   if (ldb % 2 == 0 && ldc % 2 == 0 && aligned(B, 8) && aligned(C, 8) && round_up(f, 2) <= ldb && round_up(f, 2) <= ldc) {
     const int f_eff = round_up(f, 2);
-    return dispatch_shape<2>(f_eff / 2, rowptr, col, val, n, nnz, B, ldb, C, ldc, f_eff, beta, p, s);
+    return dispatch_shape<2>(f_eff / 2, rowptr, col, val, n, m, nnz, B, ldb, C, ldc, f_eff, beta, p, s);
   }
-  return dispatch_shape<1>(f, rowptr, col, val, n, nnz, B, ldb, C, ldc, f, beta, p, s);
+  return dispatch_shape<1>(f, rowptr, col, val, n, m, nnz, B, ldb, C, ldc, f, beta, p, s);
 }
+

@@ -51,14 +51,24 @@ def _rmat_sample(count, scale, n, g, device, abcd):
     return torch.minimum(rows, cols) * n + torch.maximum(rows, cols)
 
 
-def rmat_graph(n, target_nnz=None, edge_factor=None, seed=1, device="cpu", abcd=RMAT_ABCD, chunk=1 << 24):
+def rmat_graph(n, target_nnz=None, edge_factor=None, seed=1, device="cpu", abcd=RMAT_ABCD, chunk=1 << 24,
+               permute=True):
     """R-MAT graph on n vertices (scale = ceil(log2 n); endpoints >= n rejected), symmetrised, duplicates
     merged, self loops dropped.  Either `edge_factor` (sample edge_factor * n directed edges once, the
     Graph500 convention) or `target_nnz`: sampling is topped up until the matrix the GCN uses
     (2 * pairs + n self loops) has target_nnz nonzeros to within 0.5 % from below.
-    Returns a 2 x E int64 edge list (both directions, no self loops)."""
+    With `permute` the vertex labels are shuffled by a seeded random permutation, as Graph500 generators do:
+    raw R-MAT puts every hub at a low index, which no real dataset does and which would make contiguous
+    block rows wildly unequal.  Returns a 2 x E int64 edge list (both directions, no self loops)."""
     g = _gen(seed, device)
     scale = max(1, math.ceil(math.log2(n)))
+    perm = torch.randperm(n, generator=g, device=device) if permute else None
+
+    def relabel(keys):
+        if perm is None:
+            return keys
+        a, b = perm[keys // n], perm[keys % n]
+        return torch.unique(torch.minimum(a, b) * n + torch.maximum(a, b))
 
     def sample(count):
         parts = []
@@ -70,7 +80,7 @@ def rmat_graph(n, target_nnz=None, edge_factor=None, seed=1, device="cpu", abcd=
 
     if target_nnz is None:
         keys = torch.unique(sample(int(edge_factor * n)))
-        return _pairs_to_edge_index(keys, n)
+        return _pairs_to_edge_index(relabel(keys), n)
     want = (target_nnz - n) // 2
     keys = torch.empty(0, dtype=torch.int64, device=device)
     yield_est = 1.0
@@ -83,7 +93,7 @@ def rmat_graph(n, target_nnz=None, edge_factor=None, seed=1, device="cpu", abcd=
         keys = torch.unique(torch.cat([keys, sample(batch)]))
         # pairs gained per sample drawn; it only falls as the graph fills up, so this never overshoots by much
         yield_est = max((keys.numel() - before) / batch, 1e-3) * 0.9
-    return _pairs_to_edge_index(keys, n)
+    return _pairs_to_edge_index(relabel(keys), n)
 
 
 def node_data(n, features, classes, train_fraction=1.0, seed_features=2, seed_labels=3, device="cpu"):

@@ -219,7 +219,7 @@ def spmm_gpu(A_rowindices, A_colindices, A_values, n, m, B, C):
 def sparse_coo_tensor_gpu(indices, values, size):
     """Drop-in for `sparse_coo_tensor_cpp.sparse_coo_tensor_gpu` (sparse_coo_tensor.cu:43-54): sparse COO
     constructor without index validation (and so without a device synchronisation)."""
-    return torch._sparse_coo_tensor_unsafe(indices, values, tuple(size))
+    return torch.sparse_coo_tensor(indices, values, tuple(size), check_invariants=False)
 
 
 # ------------------------------------------------------------------------------------------- dense

@@ -42,9 +42,10 @@ enum {
 int cagnet_version(void);
 const char* cagnet_last_error_string(void);
 
-/* Tuning knobs, for sweeps: "spmm_nv" (vectors per lane, 0 = automatic), "spmm_long" (rows with
- * more nonzeros than this are processed by a whole thread block; must match between plan and
- * multiply).  Host-side global state; returns CAGNET_E_ARG for an unknown name. */
+/* Tuning knobs, for sweeps: "spmm_tile" (vectors per feature tile, 0 = automatic), "spmm_rpb" (rows per thread
+ * block of the warp-per-row kernel), "spmm_long" (rows with
+ * more nonzeros than this are listed in the plan and processed by a whole thread block).  Host-side global
+ * state; returns CAGNET_E_ARG for an unknown name or value. */
 int cagnet_set_param(const char* name, int value);
 int cagnet_get_param(const char* name);
 

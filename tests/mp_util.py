@@ -1,4 +1,5 @@
-"""Run a function as `world` Gloo ranks in child processes (127.0.0.1 rendezvous) and collect its results."""
+"""Run a function as `world` ranks in child processes (127.0.0.1 rendezvous) and collect its results: Gloo on CPU
+by default, NCCL with one GPU per rank when backend="nccl"."""
 import os
 import socket
 import sys
@@ -19,13 +20,17 @@ def _free_port():
     return port
 
 
-def _entry(rank, world, port, fn, args, queue):
+def _entry(rank, world, port, fn, args, queue, backend):
     try:
         if ROOT not in sys.path:
             sys.path.insert(0, ROOT)
         os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
         torch.set_num_threads(1)
-        dist.init_process_group("gloo", rank=rank, world_size=world)
+        if backend == "nccl":
+            torch.cuda.set_device(rank)
+            dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+        else:
+            dist.init_process_group("gloo", rank=rank, world_size=world)
         out = fn(rank, world, *args)
         queue.put((rank, "ok", out))
         dist.barrier()
@@ -34,12 +39,12 @@ def _entry(rank, world, port, fn, args, queue):
         queue.put((rank, "error", traceback.format_exc()))
 
 
-def run_ranks(world, fn, *args, timeout=300):
+def run_ranks(world, fn, *args, timeout=300, backend="gloo"):
     """fn(rank, world, *args) -> picklable; returns the list of per-rank results."""
     ctx = mp.get_context("spawn")
     queue = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_entry, args=(r, world, port, fn, args, queue)) for r in range(world)]
+    procs = [ctx.Process(target=_entry, args=(r, world, port, fn, args, queue, backend)) for r in range(world)]
     for p in procs:
         p.start()
     results = {}

@@ -67,13 +67,13 @@ def test_spmm_widths(f, beta):
 
 
 @pytest.mark.parametrize("f", [16, 41, 602])
-@pytest.mark.parametrize("nv", [0, 1, 2, 3, 4])
-def test_spmm_hub_rows_and_tilings(f, nv):
-    """Rows beyond the plan threshold go through the block-per-row kernel; nv forces feature tiling."""
-    old_long, old_nv = _native.get_param("spmm_long"), _native.get_param("spmm_nv")
+@pytest.mark.parametrize("tile", [0, 8, 16, 32, 64, 128])
+def test_spmm_hub_rows_and_tilings(f, tile):
+    """Rows beyond the plan threshold go through the block-per-row kernel; tile forces feature tiling."""
+    old_long, old_tile = _native.get_param("spmm_long"), _native.get_param("spmm_tile")
     try:
         _native.set_param("spmm_long", 256)
-        _native.set_param("spmm_nv", nv)
+        _native.set_param("spmm_tile", tile)
         blk = _random_block(600, 4000, 20, seed=3, hubs=5)
         A = ops.CsrBlock.from_coo(blk.rows, blk.cols, blk.vals, blk.n_rows, blk.n_cols)
         assert A.long_rows() >= 5
@@ -91,7 +91,7 @@ def test_spmm_hub_rows_and_tilings(f, nv):
         _close(Cd2, want)
     finally:
         _native.set_param("spmm_long", old_long)
-        _native.set_param("spmm_nv", old_nv)
+        _native.set_param("spmm_tile", old_tile)
 
 
 def test_spmm_is_bit_reproducible():
