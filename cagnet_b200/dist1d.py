@@ -38,7 +38,10 @@ class Runtime:
     """Per-process settings: what the reference keeps in module globals (gcn_distr.py:53-64)."""
 
     def __init__(self, backend, activations=True, normalization=True, replication=1, timing=False, overlap=True,
-                 categories=None):
+                 categories=None, order="reference"):
+        if order not in ("reference", "min_width"):
+            raise ValueError("order must be 'reference' or 'min_width'")
+        self.order = order
         self.backend = backend
         self.activations = bool(activations)
         self.normalization = bool(normalization)
@@ -129,16 +132,36 @@ def outer_product2(rt, inputs, ag, rank, size, group):
 
 
 class GCNFunc(torch.autograd.Function):
-    """One GCN layer: out = act((A . H) . W).  gcn_distr.py:248-339, gcn_distr_15d.py:247-345."""
+    """One GCN layer: out = act((A . H) . W).  gcn_distr.py:248-339, gcn_distr_15d.py:247-345.
+
+    With `rt.order == "min_width"` (off by default) the sparse product always runs at the narrower of the two
+    widths: forward takes A . (H . W) when the layer narrows, and a widening layer's backward takes
+    grad_H = A . (dZ . W^T) and grad_W = (A . H)^T . dZ with A . H kept from the forward pass.  The results are the
+    reference's up to the order of summation; the second identity needs A = A^T, which the reference's own
+    backward already assumes by multiplying with the forward blocks (gcn_distr.py:326)."""
 
     @staticmethod
     def forward(ctx, inputs, weight, adj_matrix, am_partitions, rank, size, group, row_groups, col_groups, func, rt):
         be = rt.backend
         act = act_name(func) if rt.activations else ACT_NONE
-        z = broad_func(rt, None, am_partitions, inputs, rank, size, row_groups, col_groups, group)
-        with rt.timers.region("comp_time", "dcomp_time"):
-            out = be.mm(z, weight.detach(), act)
+        w = weight.detach()
+        narrow = rt.order == "min_width" and w.size(1) < w.size(0)
+        widen = rt.order == "min_width" and w.size(1) > w.size(0)
+        agg = None
+        if narrow:
+            with rt.timers.region("comp_time", "dcomp_time"):
+                hw = be.mm(be.as_matrix(inputs), w, ACT_NONE)
+            z = broad_func(rt, None, am_partitions, hw, rank, size, row_groups, col_groups, group)
+            with rt.timers.region("comp_time", "dcomp_time"):
+                out = be.act(z, act)
+        else:
+            z = broad_func(rt, None, am_partitions, inputs, rank, size, row_groups, col_groups, group)
+            with rt.timers.region("comp_time", "dcomp_time"):
+                out = be.mm(z, w, act)
+            if widen:
+                agg = z
         ctx.save_for_backward(inputs, weight, out)
+        ctx.agg = agg
         ctx.args = (am_partitions, rank, size, group, row_groups, col_groups, act, rt)
         return out
 
@@ -147,15 +170,24 @@ class GCNFunc(torch.autograd.Function):
         inputs, weight, out = ctx.saved_tensors
         am_partitions, rank, size, group, row_groups, col_groups, act, rt = ctx.args
         be = rt.backend
+        w = weight.detach()
+        reduce_group = col_groups[rank % rt.replication] if rt.replication > 1 else group
         # sigma'(Z) * G in closed form from the activation output (the reference re-runs the activation
         # under autograd: gcn_distr.py:312-322)
         dz = be.act_bwd(out, be.as_matrix(grad_output), act)
+        if ctx.agg is not None:
+            grad_input = None
+            if ctx.needs_input_grad[0]:
+                with rt.timers.region("comp_time", "dcomp_time"):
+                    dzw = be.mm_nt(dz, w)
+                grad_input = broad_func(rt, None, am_partitions, dzw, rank, size, row_groups, col_groups, group)
+            grad_weight = outer_product2(rt, ctx.agg, dz, rank, size, reduce_group)
+            return grad_input, grad_weight, None, None, None, None, None, None, None, None, None
         ag = broad_func(rt, None, am_partitions, dz, rank, size, row_groups, col_groups, group)
         grad_input = None
         if ctx.needs_input_grad[0]:
             with rt.timers.region("comp_time", "dcomp_time"):
-                grad_input = be.mm_nt(ag, weight.detach())
-        reduce_group = col_groups[rank % rt.replication] if rt.replication > 1 else group
+                grad_input = be.mm_nt(ag, w)
         grad_weight = outer_product2(rt, inputs, ag, rank, size, reduce_group)
         return grad_input, grad_weight, None, None, None, None, None, None, None, None, None
 

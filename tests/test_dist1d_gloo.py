@@ -10,7 +10,7 @@ import torch
 from tests.mp_util import run_ranks
 
 
-def _worker(rank, world, case_path, replication, activations, normalization, overlap):
+def _worker(rank, world, case_path, replication, activations, normalization, overlap, order="reference"):
     import numpy as np
     import torch
     from cagnet_b200 import dist1d, graphs
@@ -20,7 +20,8 @@ def _worker(rank, world, case_path, replication, activations, normalization, ove
     n, f, mid, classes, epochs = d["cfg"][:5].tolist()
     edge, x, y, mask = (torch.from_numpy(d[k]) for k in ("edge_index", "x", "y", "mask"))
     adj = graphs.add_self_loops(edge, n) if normalization else edge
-    rt = dist1d.Runtime(CpuBackend(), activations, normalization, replication, timing=False, overlap=overlap)
+    rt = dist1d.Runtime(CpuBackend(), activations, normalization, replication, timing=False, overlap=overlap,
+                        order=order)
     group, row_groups, col_groups = dist1d.make_groups(rank, world, replication)
     model = dist1d.Model(rt, rank, world, x, adj, dist1d.Data(y=y, train_mask=mask), f, classes, group, row_groups,
                          col_groups)
@@ -59,3 +60,19 @@ def test_15d_with_c1_is_the_1d_schedule(golden_dir):
     d = np.load(path)
     results = run_ranks(3, _worker, path, 1, True, True, True)
     np.testing.assert_allclose(results[1]["ep2_w1"], d["r1_ep2_w1"], rtol=1e-4, atol=2e-5)
+
+
+@pytest.mark.parametrize("name", ["train_1d_P3.npz", "train_15d_P4.npz", "train_1d_P1_plain.npz"])
+def test_min_width_order_gives_the_reference_results(golden_dir, name):
+    """A.(H.W) when the layer narrows, (A.H)^T.dZ and A.(dZ.W^T) when it widens: same numbers as the reference
+    order up to fp32 summation order (the fixture graphs are symmetric, as the reference's backward assumes)."""
+    path = os.path.join(golden_dir, name)
+    d = np.load(path)
+    n, f, mid, classes, epochs, P, c, norm, act = d["cfg"].tolist()
+    results = run_ranks(P, _worker, path, c, bool(act), bool(norm), True, "min_width")
+    for rank, res in enumerate(results):
+        for ep in range(epochs):
+            for key in ("out", "gw1", "gw2", "w1", "w2"):
+                want = d[f"r{rank}_ep{ep}_{key}"]
+                np.testing.assert_allclose(res[f"ep{ep}_{key}"], want, rtol=1e-4, atol=2e-5 * max(1.0, np.abs(want).max()),
+                                           err_msg=f"{name} rank {rank} epoch {ep} {key}")
