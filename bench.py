@@ -102,7 +102,7 @@ class ClockSampler:
 
 def build_cpu_problem(model, data_y, data_mask):
     """Host copies of exactly the tensors the GPU run uses: the normalised matrix (CSR), features, labels, mask."""
-    blk = model.am_pbyp[0]
+    blk = model.am_pbyp.groups[0].block
     n = blk.n
     M = torch.sparse_csr_tensor(blk.rowptr.cpu().long(), blk.col.cpu().long(), blk.val.cpu(), size=(n, blk.m))
     X = model.inputs_loc.cpu().contiguous()

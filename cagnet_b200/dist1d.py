@@ -38,10 +38,11 @@ class Runtime:
     """Per-process settings: what the reference keeps in module globals (gcn_distr.py:53-64)."""
 
     def __init__(self, backend, activations=True, normalization=True, replication=1, timing=False, overlap=True,
-                 categories=None, order="reference"):
+                 categories=None, order="reference", stage_groups=2):
         if order not in ("reference", "min_width"):
             raise ValueError("order must be 'reference' or 'min_width'")
         self.order = order
+        self.stage_groups = stage_groups     # launch groups per sparse product; 0 = one per stage, as the reference
         self.backend = backend
         self.activations = bool(activations)
         self.normalization = bool(normalization)
@@ -64,56 +65,96 @@ def _group_size(group):
 
 
 # ------------------------------------------------------------------------------------------ schedule
+class StageGroup:
+    """Consecutive stages of one rank multiplied in ONE launch: their H blocks are received into adjacent row
+    ranges of one buffer and the adjacency blocks are fused column-wise into one CSR block."""
+
+    def __init__(self, sources, block, rows):
+        self.sources, self.block, self.rows = sources, block, rows     # sources: [(source rank, rows of its H block)]
+
+
+class StagePlan:
+    """The stages `rank` walks through (gcn_distr_15d.py:194-208), cut into `groups` launch groups.
+
+    groups = number of stages reproduces the reference's granularity (one broadcast, one multiply per stage).
+    Fewer groups trade pipeline depth for larger multiplies: on a 233K-vertex graph split 8 ways one launch per
+    stage spends most of its time on per-launch and per-row-segment overheads (6.5 ms against 4.1 ms for the same
+    nonzeros in one launch at width 602, 1.29 ms against 0.39 ms at width 16), while the broadcasts it could hide
+    take 0.7 ms in total.  The default of two groups keeps the broadcast of the second half behind the multiply of
+    the first."""
+
+    def __init__(self, backend, blocks, rank, size, replication, groups=2):
+        stages = partition.stages_15d(rank, size, replication)
+        self.n_loc = blocks[0].n_rows
+        n_groups = max(1, min(len(stages), groups if groups and groups > 0 else len(stages)))
+        bounds = [round(i * len(stages) / n_groups) for i in range(n_groups + 1)]
+        self.groups = []
+        for a, b in zip(bounds[:-1], bounds[1:]):
+            part = stages[a:b]
+            fused = partition.fuse_columns([blocks[bid] for _, bid in part])
+            sources = [(q, blocks[bid].n_cols) for q, bid in part]
+            self.groups.append(StageGroup(sources, backend.make_block(fused), fused.n_cols))
+        self.max_rows = max(g.rows for g in self.groups) if self.groups else 0
+
+
 def broad_func(rt, node_count, am_partitions, inputs, rank, size, row_groups, col_groups, group):
     """Z_r = sum over this rank's stages of A_blk[stage] . H_stage, then (1.5D) an all-reduce of Z_r over the
-    c replicas of the block row.  gcn_distr.py:203-246, gcn_distr_15d.py:173-245.
+    c replicas of the block row.  gcn_distr.py:203-246, gcn_distr_15d.py:173-245.  `am_partitions` is the
+    rank's StagePlan.
 
-    Each stage broadcasts one block of H inside the rank's column communicator and multiplies it by the
-    cached CSR block.  Two receive buffers alternate: the broadcast of stage k+1 is issued (async) before
-    the multiply of stage k is queued, so NCCL moves block k+1 while the SMs work on block k."""
+    Every stage broadcasts one block of H inside the rank's column communicator; the stages of a launch group
+    land in one buffer and are multiplied by the group's fused CSR block.  Two buffers alternate: the broadcasts
+    of group k+1 are issued (async) before the multiply of group k is queued, so NCCL moves the next blocks while
+    the SMs work on the current ones."""
     be, c = rt.backend, rt.replication
+    plan = am_partitions
     inputs = be.as_matrix(inputs)
     f = inputs.size(1)
-    stages = partition.stages_15d(rank, size, c)
     rank_c, rank_col = rank // c, rank % c
     col_group = col_groups[rank_col] if c > 1 else group
     row_group = row_groups[rank_c] if c > 1 else None
     comm = size > 1 and dist.is_initialized()
-    n_loc = be.block_shape(am_partitions[0])[0]
-    z = be.empty(n_loc, f)
-    if not stages:
+    z = be.empty(plan.n_loc, f)
+    if not plan.groups:
         be.wire(z).zero_()
-    max_rows = max(be.block_shape(b)[1] for b in am_partitions)
     bufs = [None, None]
 
-    def post(i):
-        q, bid = stages[i]
-        rows = be.block_shape(am_partitions[bid])[1]
-        if q == rank:
-            tensor = inputs
+    def post(gi):
+        g = plan.groups[gi]
+        if len(g.sources) == 1 and g.sources[0][0] == rank:
+            tensor, pieces = inputs, [(inputs, rank)]
         else:
-            if bufs[i % 2] is None:
-                bufs[i % 2] = be.empty(max_rows, f)
-            tensor = bufs[i % 2][:rows]
-        rt.timers.count("bcast_words", rows * f)
-        work = dist.broadcast(be.wire(tensor), src=q, group=col_group, async_op=True) if comm else None
-        return tensor, work
+            if bufs[gi % 2] is None:
+                bufs[gi % 2] = be.empty(plan.max_rows, f)
+            tensor, pieces, off = bufs[gi % 2][:g.rows], [], 0
+            for q, rows in g.sources:
+                piece = tensor[off:off + rows]
+                if q == rank:
+                    be.wire(piece).copy_(be.wire(inputs))       # this rank's own block takes its place in the buffer
+                pieces.append((piece, q))
+                off += rows
+        works = []
+        for piece, q in pieces:
+            rt.timers.count("bcast_words", piece.size(0) * f)
+            if comm:
+                works.append(dist.broadcast(be.wire(piece), src=q, group=col_group, async_op=True))
+        return tensor, works
 
     serial = rt.timers.enabled or not rt.overlap
     pending = None
-    for i, (q, bid) in enumerate(stages):
+    for gi, g in enumerate(plan.groups):
         if serial:
             with rt.timers.region("comm_time", "bcast_comm_time"):
-                tensor, work = post(i)
-                if work is not None:
-                    work.wait()
+                tensor, works = post(gi)
+                for w in works:
+                    w.wait()
         else:
-            tensor, work = pending if pending is not None else post(i)
-            pending = post(i + 1) if i + 1 < len(stages) else None
-            if work is not None:
-                work.wait()                      # stream-side wait: the host runs ahead
+            tensor, works = pending if pending is not None else post(gi)
+            pending = post(gi + 1) if gi + 1 < len(plan.groups) else None
+            for w in works:
+                w.wait()                         # stream-side wait: the host runs ahead
         with rt.timers.region("comp_time", "scomp_time"):
-            be.spmm(am_partitions[bid], tensor, z, 0.0 if i == 0 else 1.0)
+            be.spmm(g.block, tensor, z, 0.0 if gi == 0 else 1.0)
     if c > 1 and comm:
         with rt.timers.region("comm_time", "reduce_comm_time"):
             dist.all_reduce(be.wire(z), op=dist.ReduceOp.SUM, group=row_group)
@@ -222,7 +263,7 @@ class Model:
         self.node_count = node_count
         inputs_loc, blocks = partition.oned_partition(rank, size, inputs, adj_matrix, rt.normalization, c)
         self.inputs_loc = be.as_matrix(inputs_loc)
-        self.am_pbyp = [be.make_block(b) for b in blocks]
+        self.am_pbyp = StagePlan(be, blocks, rank, size, c, rt.stage_groups)
         n_per_proc = int(math.ceil(float(node_count) / (size / c)))
         rank_c = rank // c
         lo, hi = rank_c * n_per_proc, min(node_count, (rank_c + 1) * n_per_proc)

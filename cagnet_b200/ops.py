@@ -24,6 +24,24 @@ def _stream():
     return torch.cuda.current_stream().cuda_stream
 
 
+class _NoSwitch:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        return False
+
+
+_NO_SWITCH = _NoSwitch()
+
+
+def _on(device):
+    """Context that makes `device` current for a launch; free when it already is (the common case)."""
+    if device.index is None or device.index == torch.cuda.current_device():
+        return _NO_SWITCH
+    return torch.cuda.device(device)
+
+
 def pad_ld(f):
     """Leading dimension used for matrices this package allocates: rows start on a 16-byte boundary
     (128-bit loads) and, for wide rows, on a 128-byte cache line."""
@@ -112,7 +130,7 @@ def coo2csr(rows, n):
         raise RuntimeError("cagnet_b200: coo2csr needs a 1-D int32 CUDA tensor")
     rows = rows.contiguous()
     rowptr = torch.empty(n + 1, dtype=torch.int32, device=rows.device)
-    with torch.cuda.device(rows.device):
+    with _on(rows.device):
         _native.check(_native.lib().cagnet_coo2csr_i32(rows.data_ptr(), rows.numel(), n, rowptr.data_ptr(), _stream()),
                       "coo2csr")
     LAUNCHES[0] += 1
@@ -149,7 +167,7 @@ class CsrBlock:
     def validate(self, rows=None):
         """Device-side check of the block (and of the sorted COO row indices it came from); one readback."""
         status = torch.zeros(1, dtype=torch.int32, device=self.val.device)
-        with torch.cuda.device(self.val.device):
+        with _on(self.val.device):
             _native.check(_native.lib().cagnet_check_csr_i32(self.rowptr.data_ptr(), self.col.data_ptr(),
                                                              None if rows is None else rows.data_ptr(), self.n, self.m,
                                                              self.nnz, status.data_ptr(), _stream()), "check_csr")
@@ -164,7 +182,7 @@ class CsrBlock:
     def build_plan(self):
         nbytes = _native.lib().cagnet_spmm_plan_bytes(self.n, self.nnz)
         self.plan = torch.empty((nbytes + 15) // 16 * 16, dtype=torch.uint8, device=self.val.device)
-        with torch.cuda.device(self.val.device):
+        with _on(self.val.device):
             _native.check(_native.lib().cagnet_spmm_plan_i32(self.rowptr.data_ptr(), self.n, self.nnz,
                                                              self.plan.data_ptr(), self.plan.numel(), _stream()),
                           "spmm_plan")
@@ -188,7 +206,7 @@ def spmm(block, B, C, beta=1.0):
                            % (block.n, block.m, tuple(B.shape), tuple(C.shape)))
     if B.device != block.val.device or C.device != block.val.device:
         raise RuntimeError("cagnet_b200: spmm operands on different devices")
-    with torch.cuda.device(C.device):
+    with _on(C.device):
         _native.check(_native.lib().cagnet_spmm_csr_f32(
             block.rowptr.data_ptr(), block.col.data_ptr(), block.val.data_ptr(), block.n, block.m, block.nnz,
             B.data_ptr(), ldb, C.data_ptr(), ldc, B.size(1), float(beta),
@@ -239,7 +257,7 @@ def gemm_nn(X, W, trans_w=False, epilogue=EPI_NONE, aux=None, out=None):
         out = empty_padded(X.size(0), N, X.device)
     ldz = _ld(out, "out")
     aux_ptr, ldaux = (None, 0) if aux is None else (aux.data_ptr(), _ld(aux, "aux"))
-    with torch.cuda.device(X.device):
+    with _on(X.device):
         _native.check(_native.lib().cagnet_gemm_nn_f32(X.data_ptr(), ldx, W.data_ptr(), ldw, int(bool(trans_w)),
                                                        out.data_ptr(), ldz, X.size(0), K, N, int(epilogue), aux_ptr,
                                                        ldaux, _stream()), "gemm_nn")
@@ -263,7 +281,7 @@ def gemm_tn(H, G, out=None, accumulate=False):
     ldo = _ld(out, "out")
     nbytes = _native.lib().cagnet_gemm_tn_workspace_bytes(n, K, N)
     ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=H.device)
-    with torch.cuda.device(H.device):
+    with _on(H.device):
         _native.check(_native.lib().cagnet_gemm_tn_f32(H.data_ptr(), ldh, G.data_ptr(), ldg, out.data_ptr(), ldo,
                                                        n, K, N, 1.0 if accumulate else 0.0, ws.data_ptr(), ws.numel(),
                                                        _stream()), "gemm_tn")
@@ -277,7 +295,7 @@ ROW_MAX, ROW_SUM, ROW_SUMEXP = 0, 1, 2
 def row_reduce(z, mode, ref=None):
     """Per-row max / sum / sum of exp(z - ref) over the columns of z: fp32 vector of n entries."""
     out = torch.empty(z.size(0), dtype=torch.float32, device=z.device)
-    with torch.cuda.device(z.device):
+    with _on(z.device):
         _native.check(_native.lib().cagnet_row_reduce_f32(z.data_ptr(), _ld(z, "z"), z.size(0), z.size(1), int(mode),
                                                           None if ref is None else ref.data_ptr(), out.data_ptr(),
                                                           _stream()), "row_reduce")
@@ -287,7 +305,7 @@ def row_reduce(z, mode, ref=None):
 
 def log_softmax_apply(z, row_max, row_sum):
     out = empty_padded(z.size(0), z.size(1), z.device)
-    with torch.cuda.device(z.device):
+    with _on(z.device):
         _native.check(_native.lib().cagnet_log_softmax_apply_f32(z.data_ptr(), _ld(z, "z"), row_max.data_ptr(),
                                                                  row_sum.data_ptr(), out.data_ptr(), _ld(out, "out"),
                                                                  z.size(0), z.size(1), _stream()), "log_softmax_apply")
@@ -297,7 +315,7 @@ def log_softmax_apply(z, row_max, row_sum):
 
 def log_softmax_bwd_apply(logp, g, row_sum_g):
     out = empty_padded(logp.size(0), logp.size(1), logp.device)
-    with torch.cuda.device(logp.device):
+    with _on(logp.device):
         _native.check(_native.lib().cagnet_log_softmax_bwd_apply_f32(
             logp.data_ptr(), _ld(logp, "logp"), g.data_ptr(), _ld(g, "g"), row_sum_g.data_ptr(), out.data_ptr(),
             _ld(out, "out"), logp.size(0), logp.size(1), _stream()), "log_softmax_bwd_apply")
@@ -307,7 +325,7 @@ def log_softmax_bwd_apply(logp, g, row_sum_g):
 
 def relu(z):
     out = empty_padded(z.size(0), z.size(1), z.device)
-    with torch.cuda.device(z.device):
+    with _on(z.device):
         _native.check(_native.lib().cagnet_relu_fwd_f32(z.data_ptr(), _ld(z, "z"), out.data_ptr(), _ld(out, "out"),
                                                         z.size(0), z.size(1), _stream()), "relu_fwd")
     LAUNCHES[0] += 1
@@ -316,7 +334,7 @@ def relu(z):
 
 def relu_bwd(h, g):
     out = empty_padded(h.size(0), h.size(1), h.device)
-    with torch.cuda.device(h.device):
+    with _on(h.device):
         _native.check(_native.lib().cagnet_relu_bwd_f32(h.data_ptr(), _ld(h, "h"), g.data_ptr(), _ld(g, "g"),
                                                         out.data_ptr(), _ld(out, "out"), h.size(0), h.size(1),
                                                         _stream()), "relu_bwd")
@@ -326,7 +344,7 @@ def relu_bwd(h, g):
 
 def log_softmax(z):
     out = empty_padded(z.size(0), z.size(1), z.device)
-    with torch.cuda.device(z.device):
+    with _on(z.device):
         _native.check(_native.lib().cagnet_log_softmax_fwd_f32(z.data_ptr(), _ld(z, "z"), out.data_ptr(),
                                                                _ld(out, "out"), z.size(0), z.size(1), _stream()),
                       "log_softmax_fwd")
@@ -336,7 +354,7 @@ def log_softmax(z):
 
 def log_softmax_bwd(logp, g):
     out = empty_padded(logp.size(0), logp.size(1), logp.device)
-    with torch.cuda.device(logp.device):
+    with _on(logp.device):
         _native.check(_native.lib().cagnet_log_softmax_bwd_f32(logp.data_ptr(), _ld(logp, "logp"), g.data_ptr(),
                                                                _ld(g, "g"), out.data_ptr(), _ld(out, "out"),
                                                                logp.size(0), logp.size(1), _stream()),
@@ -358,7 +376,7 @@ def nll_masked(logp, y, mask, count, cls_lo=0, cls_hi=None, scale=1.0, want_grad
     grad = empty_padded(n, N, logp.device) if want_grad else None
     nbytes = _native.lib().cagnet_nll_workspace_bytes(n)
     ws = torch.empty(nbytes, dtype=torch.uint8, device=logp.device)
-    with torch.cuda.device(logp.device):
+    with _on(logp.device):
         _native.check(_native.lib().cagnet_nll_masked_f32(
             logp.data_ptr(), _ld(logp, "logp"), y.data_ptr(), mask_u8.data_ptr(), n, N, int(cls_lo), int(cls_hi),
             float(count), float(scale), loss.data_ptr(), None if grad is None else grad.data_ptr(),

@@ -58,6 +58,23 @@ def coalesce_block(r, c, n_rows, n_cols, d_row=None, d_col=None):
     return Block(rows, cols, vals, int(n_rows), int(n_cols))
 
 
+def fuse_columns(blocks):
+    """[B0 | B1 | ...]: blocks with the same row count side by side as one coalesced block."""
+    if len(blocks) == 1:
+        return blocks[0]
+    n_rows = blocks[0].n_rows
+    offs = [0]
+    for b in blocks:
+        if b.n_rows != n_rows:
+            raise ValueError("fuse_columns: blocks differ in row count")
+        offs.append(offs[-1] + b.n_cols)
+    rows = torch.cat([b.rows for b in blocks])
+    cols = torch.cat([b.cols + o for b, o in zip(blocks, offs)])
+    vals = torch.cat([b.vals for b in blocks])
+    order = torch.argsort(rows * offs[-1] + cols)
+    return Block(rows[order], cols[order], vals[order], n_rows, offs[-1])
+
+
 def _in_range(x, lo, hi):
     return (x >= lo) & (x < hi)
 

@@ -10,7 +10,8 @@ import torch
 from tests.mp_util import run_ranks
 
 
-def _worker(rank, world, case_path, replication, activations, normalization, overlap, order="reference"):
+def _worker(rank, world, case_path, replication, activations, normalization, overlap, order="reference",
+            stage_groups=2):
     import numpy as np
     import torch
     from cagnet_b200 import dist1d, graphs
@@ -21,7 +22,7 @@ def _worker(rank, world, case_path, replication, activations, normalization, ove
     edge, x, y, mask = (torch.from_numpy(d[k]) for k in ("edge_index", "x", "y", "mask"))
     adj = graphs.add_self_loops(edge, n) if normalization else edge
     rt = dist1d.Runtime(CpuBackend(), activations, normalization, replication, timing=False, overlap=overlap,
-                        order=order)
+                        order=order, stage_groups=stage_groups)
     group, row_groups, col_groups = dist1d.make_groups(rank, world, replication)
     model = dist1d.Model(rt, rank, world, x, adj, dist1d.Data(y=y, train_mask=mask), f, classes, group, row_groups,
                          col_groups)
@@ -37,14 +38,17 @@ def _worker(rank, world, case_path, replication, activations, normalization, ove
     return out
 
 
-@pytest.mark.parametrize("name,overlap", [("train_1d_P1.npz", True), ("train_1d_P3.npz", True),
-                                          ("train_1d_P3.npz", False), ("train_1d_P1_plain.npz", True),
-                                          ("train_15d_P4.npz", True), ("train_15d_P8.npz", True)])
-def test_schedule_matches_reference_fixture(golden_dir, name, overlap):
+@pytest.mark.parametrize("name,overlap,groups", [("train_1d_P1.npz", True, 2), ("train_1d_P3.npz", True, 0),
+                                                 ("train_1d_P3.npz", False, 2), ("train_1d_P3.npz", True, 1),
+                                                 ("train_1d_P1_plain.npz", True, 2), ("train_15d_P4.npz", True, 2),
+                                                 ("train_15d_P8.npz", True, 0), ("train_15d_P8.npz", True, 2)])
+def test_schedule_matches_reference_fixture(golden_dir, name, overlap, groups):
+    """groups = 0: one broadcast + one multiply per stage (the reference's granularity); 1: all stages in one
+    launch; 2: the default two launch groups."""
     path = os.path.join(golden_dir, name)
     d = np.load(path)
     n, f, mid, classes, epochs, P, c, norm, act = d["cfg"].tolist()
-    results = run_ranks(P, _worker, path, c, bool(act), bool(norm), overlap)
+    results = run_ranks(P, _worker, path, c, bool(act), bool(norm), overlap, "reference", groups)
     for rank, res in enumerate(results):
         for ep in range(epochs):
             for key in ("out", "gw1", "gw2", "w1", "w2"):

@@ -82,7 +82,7 @@ def test_power_law_graph_epoch_and_linearity():
         # X^T (A dZ) sums 30,000 signed terms per entry and cancels to ~1e-3: fp32 rounding of the terms shows
         # at a few 1e-4 of the result whatever the order of summation
         assert e_g <= 1e-3, ("weight gradient", ep, e_g)
-    A = model.am_pbyp[0]
+    A = model.am_pbyp.groups[0].block
     b1, b2 = ops.to_padded(torch.randn(n, 41, device="cuda")), ops.to_padded(torch.randn(n, 41, device="cuda"))
     c1, c2, c12 = (ops.zeros_padded(n, 41, "cuda") for _ in range(3))
     ops.spmm(A, b1, c1, 0.0)
