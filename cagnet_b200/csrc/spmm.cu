@@ -378,3 +378,74 @@ extern "C" int cagnet_spmm_csr_f32(const int32_t* rowptr, const int32_t* col, co
   return dispatch_shape<1>(f, rowptr, col, val, n, m, nnz, B, ldb, C, ldc, f, beta, p, s);
 }
 
+// ------------------------------------------------------------------------------------------------
+// A multiply for callers that must not allocate.
+//
+// The ordinary entry point wants a plan buffer, which somebody has to allocate.  Some hosts cannot do that at
+// the point of the call: a serving process whose device memory was handed, all of it, to another allocator at
+// start-up (cudaMalloc then simply fails), or a latency-critical loop that may not take the implicit device
+// synchronisation and driver lock that cudaMalloc/cudaFree bring with them.  For them the plan lives in the
+// fixed device array below, which is part of the library image: every GPU that loads the library holds these
+// 256 KB from load until exit whether or not the entry point is ever used.
+namespace cagnet {
+
+constexpr int kStaticPlanRows = 65536;   // at most this many hub rows can be listed
+static __device__ __align__(256) int g_static_plan[kPlanHeaderInts + kStaticPlanRows];
+
+// In host code `g_static_plan` is only a handle for the runtime, not a device address; the address has to be
+// asked for, per device, with that device current.  Cached here after the first call on each device.
+constexpr int kMaxDevices = 64;
+static int* g_static_plan_addr[kMaxDevices] = {};
+
+static int static_plan_address(int** out) {
+  int device = -1;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess || device < 0 || device >= kMaxDevices)
+    return fail(CAGNET_E_LAUNCH, "cagnet_spmm_csr_f32_noalloc: cannot identify the current device%s (%lld)", "",
+                static_cast<long long>(device));
+  if (!g_static_plan_addr[device]) {
+    int* p = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_static_plan);
+    if (e != cudaSuccess || !p) {
+      snprintf(last_error_buf(), 256, "cagnet_spmm_csr_f32_noalloc: cudaGetSymbolAddress failed: %s",
+               cudaGetErrorString(e));
+      return CAGNET_E_LAUNCH;
+    }
+    g_static_plan_addr[device] = p;
+  }
+  *out = g_static_plan_addr[device];
+  return CAGNET_OK;
+}
+
+}  // namespace cagnet
+
+extern "C" int64_t cagnet_spmm_noalloc_max_nnz(void) {
+  // the hub-row list can never hold more than nnz / threshold + 1 rows, so this many nonzeros always fit
+  return static_cast<int64_t>(kStaticPlanRows - 1) * g_tuning.spmm_long;
+}
+
+extern "C" int cagnet_spmm_csr_f32_noalloc(const int32_t* rowptr, const int32_t* col, const float* val, int32_t n,
+                                           int32_t m, int64_t nnz, const float* B, int64_t ldb, float* C, int64_t ldc,
+                                           int32_t f, float beta, void* stream) {
+  if (n < 0 || m < 0 || nnz < 0 || f < 0) return fail(CAGNET_E_ARG, "cagnet_spmm_csr_f32_noalloc: negative size");
+  if (n == 0 || f == 0) return CAGNET_OK;
+  if (!rowptr) return fail(CAGNET_E_ARG, "cagnet_spmm_csr_f32_noalloc: null pointer");
+  if (nnz > INT_MAX) return fail(CAGNET_E_OVERFLOW, "cagnet_spmm_csr_f32_noalloc: nnz %s%lld exceeds int32", "", nnz);
+  if (nnz > cagnet_spmm_noalloc_max_nnz())
+    return fail(CAGNET_E_WORKSPACE,
+                "cagnet_spmm_csr_f32_noalloc: %s%lld nonzeros exceed the built-in scratch (at most %lld at the current "
+                "hub-row threshold); use cagnet_spmm_csr_f32 with a caller-allocated plan",
+                "", nnz, static_cast<long long>(cagnet_spmm_noalloc_max_nnz()));
+  int* plan = nullptr;
+  const int rc = static_plan_address(&plan);
+  if (rc != CAGNET_OK) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int threshold = g_tuning.spmm_long;
+  const int capacity = min(plan_capacity(nnz, threshold), kStaticPlanRows);
+  // the array keeps whatever the previous call left in it: the header kernel resets the row count first
+  spmm_plan_header_kernel<<<1, 1, 0, s>>>(threshold, capacity, plan);
+  spmm_plan_kernel<<<(n + 255) / 256, 256, 0, s>>>(rowptr, n, threshold, capacity, plan);
+  const int lrc = check_launch("cagnet_spmm_csr_f32_noalloc");
+  if (lrc != CAGNET_OK) return lrc;
+  return cagnet_spmm_csr_f32(rowptr, col, val, n, m, nnz, B, ldb, C, ldc, f, beta, plan, stream);
+}

@@ -81,6 +81,26 @@ int cagnet_spmm_csr_f32(const int32_t* rowptr, const int32_t* col, const float* 
                         const float* B, int64_t ldb, float* C, int64_t ldc, int32_t f, float beta,
                         const void* plan, void* stream);
 
+/* ---- The same multiply for callers that cannot allocate device memory (no counterpart in the reference,
+ * whose op calls cudaMalloc twice per call: sparse_coo_tensor.cu:136, 213).  Meant for hosts where every byte
+ * of the GPU already belongs to another allocator, so that cudaMalloc fails, or where the device-wide
+ * synchronisation hidden in cudaMalloc/cudaFree is not acceptable inside the loop that calls this.  The
+ * hub-row list is built, on `stream`, in a fixed 256 KB device array that is part of the library (each GPU
+ * that loads the library holds it until the process exits), then the multiply runs exactly as
+ * cagnet_spmm_csr_f32 does with a plan.  Nothing is allocated or freed, here or in anything it calls.
+ *   - Limit: nnz <= cagnet_spmm_noalloc_max_nnz() (65,535 x the hub-row threshold: about 268 M at the default
+ *     4096); beyond it the call returns CAGNET_E_WORKSPACE and does nothing.
+ *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that
+ *     device current); make that first call before starting any stream capture.
+ *   - All calls share the one array and the array keeps the last call's list: each call resets it first, and
+ *     two calls whose kernels can overlap on the GPU (different streams, different host threads) race on it.
+ *     Serialise them, or use cagnet_spmm_csr_f32 with one plan per block. */
+int64_t cagnet_spmm_noalloc_max_nnz(void);
+int cagnet_spmm_csr_f32_noalloc(const int32_t* rowptr, const int32_t* col, const float* val,
+                                int32_t n, int32_t m, int64_t nnz,
+                                const float* B, int64_t ldb, float* C, int64_t ldc, int32_t f, float beta,
+                                void* stream);
+
 /* ---- Z = epilogue(X * W) for a tall X (n x K, ldx) and a small W.
  * transW = 0: W is K x N row-major (ldw);  transW = 1: W is N x K row-major (ldw) and is used
  * transposed (the `mm(ag, weight.t())` form).  aux (n x N, ldaux) is read by CAGNET_EPI_RELU_MASK only.
