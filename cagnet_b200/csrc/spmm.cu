@@ -242,7 +242,7 @@ __global__ void spmm_plan_header_kernel(int threshold, int capacity, int* plan) 
 static int plan_capacity(int64_t nnz, int threshold) { return static_cast<int>(nnz / threshold) + 1; }
 
 template <int VEC, int LPN, int NV>
-static int launch_spmm(const int* rowptr, const int* col, const float* val, int n, int64_t nnz, const float* B,
+static int launch_spmm(const int* rowptr, const int* col, const float* val, int n, int m, int64_t nnz, const float* B,
                        int64_t ldb, float* C, int64_t ldc, int f_eff, float beta, const int* plan,
                        cudaStream_t stream) {
   constexpr int TILE = LPN * VEC * NV;
@@ -277,9 +277,8 @@ static int dispatch_shape(int vectors, const int* rowptr, const int* col, const 
                           const float* B, int64_t ldb, float* C, int64_t ldc, int f_eff, float beta, const int* plan,
                           cudaStream_t stream) {
 #define CAGNET_SPMM_CASE(LPN, NV) \
-  return launch_spmm<VEC, LPN, NV>(rowptr, col, val, n, nnz, B, ldb, C, ldc, f_eff, beta, plan, stream)
+  return launch_spmm<VEC, LPN, NV>(rowptr, col, val, n, m, nnz, B, ldb, C, ldc, f_eff, beta, plan, stream)
   int tile = g_tuning.spmm_tile > 0 ? g_tuning.spmm_tile : auto_tile(vectors);
-  (void)m;
   if (vectors <= 4) tile = 4;
   switch (tile) {
     case 4: CAGNET_SPMM_CASE(4, 1);

@@ -36,6 +36,11 @@ def parse_args(algorithm, argv=None):
     p.add_argument("--seed", type=int, default=1, help="seed of the synthetic graph")
     p.add_argument("--overlap", type=str, default="True", help="overlap the broadcast of block k+1 with the SpMM of block k")
     p.add_argument("--backend", type=str, default="nccl", help="torch.distributed backend (nccl)")
+    p.add_argument("--order", type=str, default="reference", choices=["reference", "min_width"],
+                   help="min_width: run every sparse product at the narrower of a layer's two widths")
+    p.add_argument("--collective", type=str, default="all_gather", choices=["all_gather", "broadcast"],
+                   help="1D: move H blocks with one all-gather per launch group, or one broadcast per source rank")
+    p.add_argument("--stagegroups", type=int, default=2, help="launch groups per sparse product (0 = one per stage)")
     args = p.parse_args(argv)
     print(args)
     missing = [k for k in ("epochs", "graphname", "timing", "midlayer", "runcount") if getattr(args, k) is None]

@@ -11,7 +11,7 @@ from tests.mp_util import run_ranks
 
 
 def _worker(rank, world, case_path, replication, activations, normalization, overlap, order="reference",
-            stage_groups=2):
+            stage_groups=2, collective="all_gather"):
     import numpy as np
     import torch
     from cagnet_b200 import dist1d, graphs
@@ -22,7 +22,7 @@ def _worker(rank, world, case_path, replication, activations, normalization, ove
     edge, x, y, mask = (torch.from_numpy(d[k]) for k in ("edge_index", "x", "y", "mask"))
     adj = graphs.add_self_loops(edge, n) if normalization else edge
     rt = dist1d.Runtime(CpuBackend(), activations, normalization, replication, timing=False, overlap=overlap,
-                        order=order, stage_groups=stage_groups)
+                        order=order, stage_groups=stage_groups, collective=collective)
     group, row_groups, col_groups = dist1d.make_groups(rank, world, replication)
     model = dist1d.Model(rt, rank, world, x, adj, dist1d.Data(y=y, train_mask=mask), f, classes, group, row_groups,
                          col_groups)
@@ -38,17 +38,21 @@ def _worker(rank, world, case_path, replication, activations, normalization, ove
     return out
 
 
-@pytest.mark.parametrize("name,overlap,groups", [("train_1d_P1.npz", True, 2), ("train_1d_P3.npz", True, 0),
-                                                 ("train_1d_P3.npz", False, 2), ("train_1d_P3.npz", True, 1),
-                                                 ("train_1d_P1_plain.npz", True, 2), ("train_15d_P4.npz", True, 2),
-                                                 ("train_15d_P8.npz", True, 0), ("train_15d_P8.npz", True, 2)])
-def test_schedule_matches_reference_fixture(golden_dir, name, overlap, groups):
-    """groups = 0: one broadcast + one multiply per stage (the reference's granularity); 1: all stages in one
-    launch; 2: the default two launch groups."""
+@pytest.mark.parametrize("name,overlap,groups,collective", [
+    ("train_1d_P1.npz", True, 2, "all_gather"), ("train_1d_P3.npz", True, 0, "broadcast"),
+    ("train_1d_P3.npz", False, 2, "broadcast"), ("train_1d_P3.npz", True, 1, "broadcast"),
+    ("train_1d_P3.npz", True, 2, "all_gather"), ("train_1d_P3.npz", False, 1, "all_gather"),
+    ("train_1d_P3.npz", True, 5, "all_gather"),
+    ("train_1d_P1_plain.npz", True, 2, "all_gather"), ("train_15d_P4.npz", True, 2, "all_gather"),
+    ("train_15d_P8.npz", True, 0, "broadcast"), ("train_15d_P8.npz", True, 2, "broadcast")])
+def test_schedule_matches_reference_fixture(golden_dir, name, overlap, groups, collective):
+    """broadcast with groups = 0: one broadcast + one multiply per stage (the reference's granularity); 1: all
+    stages in one launch; 2: two launch groups.  all_gather: the 1D blocks travel in one collective per launch
+    group (the fixture's last block is shorter than the others, so the padding path is exercised)."""
     path = os.path.join(golden_dir, name)
     d = np.load(path)
     n, f, mid, classes, epochs, P, c, norm, act = d["cfg"].tolist()
-    results = run_ranks(P, _worker, path, c, bool(act), bool(norm), overlap, "reference", groups)
+    results = run_ranks(P, _worker, path, c, bool(act), bool(norm), overlap, "reference", groups, collective)
     for rank, res in enumerate(results):
         for ep in range(epochs):
             for key in ("out", "gw1", "gw2", "w1", "w2"):
