@@ -2,7 +2,7 @@
 //
 // Work decomposition
 //   * one warp per CSR row for ordinary rows; the warp reads the row's (col, val) pairs 32 at a
-//     time with one coalesced load per array and hands them round with warp shuffles;
+//     time with one coalesced load per array and shares them through a 256-byte shared-memory stage;
 //   * LPN lanes cover one gathered row of B with VEC-wide vectors (VEC = 4 -> 128-bit loads), so a
 //     warp works on 32/LPN nonzeros at once: narrow B (f = 16) keeps all 32 lanes busy;
 //   * NV vectors per lane make a feature tile of LPN*VEC*NV columns; wider B is covered by
@@ -21,7 +21,8 @@ namespace cagnet {
 struct Tuning {
   int spmm_tile = 0;     // vectors per feature tile: 0 = automatic, else 4, 8, 16, 32, 64, 96, 128 or 160
   int spmm_rpb = 4;      // rows (warps) per thread block of the warp-per-row kernel: 1, 2, 4 or 8
-  int spmm_long = 4096;  // rows with more nonzeros go to the block-per-row kernel
+  int spmm_long = 2048;         // rows with more nonzeros are listed in the plan (block-per-row kernel)
+  int spmm_long_narrow = 4096;  // ... but products narrower than 32 vectors only hand over rows beyond this
 };
 static Tuning g_tuning;
 
@@ -56,55 +57,74 @@ __device__ __forceinline__ void store_vec(float* p, const float (&x)[VEC]) {
 }
 
 // Accumulates sum_e val[e] * B[col[e], tile columns of this lane] over e in [start, end) into acc.
-// bt already points at column (tile0 + l*VEC) of row 0 of B; vector k of the lane sits
-// k*LPN*VEC columns further on and is live iff k < nvalid.
+// bt already points at column (tile0 + l*VEC) of row 0 of B; vector k of the lane sits k*LPN*VEC columns
+// further on and is live iff k < nvalid.
+//
+// The warp reads 32 (col, val) pairs with two coalesced loads and parks them in its 256-byte slice of shared
+// memory (`stage`); every lane then needs every pair, and gets two of them per 128-bit broadcast read.  Per
+// nonzero and warp that leaves half a shared-memory read, one widening multiply-add for the row address, one
+// 128-bit gather and the FMAs -- the first version handed the pairs round with two warp shuffles per nonzero
+// and a 64-bit multiply, 22 instructions per nonzero, and ran at half of the issue rate without saturating
+// either L2 or HBM.
 template <int VEC, int LPN, int NV>
 __device__ __forceinline__ void accumulate_range(const int* __restrict__ col, const float* __restrict__ val,
-                                                 int start, int end, const float* __restrict__ bt, int64_t ldb,
-                                                 int nvalid, int lane, float (&acc)[NV][VEC]) {
+                                                 int start, int end, const float* __restrict__ bt, int ldb,
+                                                 int nvalid, int lane, int2* stage, float (&acc)[NV][VEC]) {
   constexpr int G = 32 / LPN;                      // nonzeros in flight per warp step
-  constexpr int UNROLL = (NV >= 4) ? 2 : (NV >= 2 ? 4 : 8);
+#ifndef CAGNET_SPMM_UNROLL
+#define CAGNET_SPMM_UNROLL 8
+#endif
+  constexpr int UNROLL = (NV >= 4) ? 1 : (NV >= 2 ? 2 : CAGNET_SPMM_UNROLL);
   const int sub = lane / LPN;
-  for (int base = start; base < end; base += 32) {
-    const int e = base + lane;
-    int c = 0;
-    float v = 0.f;
-    if (e < end) {
-      c = __ldg(col + e);
-      v = __ldg(val + e);
+
+  auto gather = [&](int c, float v) {
+    const float* bp = bt + static_cast<int64_t>(c) * ldb;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      if (k < nvalid) {
+        float x[VEC];
+        load_vec<VEC>(bp + k * (LPN * VEC), x);
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) acc[k][j] = fmaf(v, x[j], acc[k][j]);
+      }
     }
+  };
+
+  auto load_pair = [&](int e) {
+    int2 p = make_int2(0, 0);
+    if (e < end) {
+      p.x = __ldg(col + e);
+      p.y = __float_as_int(__ldg(val + e));
+    }
+    return p;
+  };
+  int2 next = load_pair(start + lane);
+  for (int base = start; base < end; base += 32) {
+    __syncwarp();            // every lane is done with the previous chunk
+    stage[lane] = next;
+    __syncwarp();
+    next = load_pair(base + 32 + lane);   // the following chunk's pairs travel while this one is being gathered
     const int cnt = min(32, end - base);
     if (cnt == 32) {
+      if constexpr (G == 1) {
 #pragma unroll UNROLL
-      for (int s = 0; s < 32; s += G) {
-        const int cc = __shfl_sync(0xffffffffu, c, s + sub);
-        const float vv = __shfl_sync(0xffffffffu, v, s + sub);
-        const float* bp = bt + static_cast<int64_t>(cc) * ldb;
-#pragma unroll
-        for (int k = 0; k < NV; ++k) {
-          if (k < nvalid) {
-            float x[VEC];
-            load_vec<VEC>(bp + k * (LPN * VEC), x);
-#pragma unroll
-            for (int j = 0; j < VEC; ++j) acc[k][j] = fmaf(vv, x[j], acc[k][j]);
-          }
+        for (int s = 0; s < 32; s += 2) {
+          const int4 q = *reinterpret_cast<const int4*>(stage + s);
+          gather(q.x, __int_as_float(q.y));
+          gather(q.z, __int_as_float(q.w));
+        }
+      } else {
+#pragma unroll 4
+        for (int s = 0; s < 32; s += G) {
+          const int2 q = stage[s + sub];
+          gather(q.x, __int_as_float(q.y));
         }
       }
     } else {
       for (int s = 0; s < cnt; s += G) {
-        const int cc = __shfl_sync(0xffffffffu, c, (s + sub) & 31);
-        const float vv = __shfl_sync(0xffffffffu, v, (s + sub) & 31);
         if (s + sub < cnt) {
-          const float* bp = bt + static_cast<int64_t>(cc) * ldb;
-#pragma unroll
-          for (int k = 0; k < NV; ++k) {
-            if (k < nvalid) {
-              float x[VEC];
-              load_vec<VEC>(bp + k * (LPN * VEC), x);
-#pragma unroll
-              for (int j = 0; j < VEC; ++j) acc[k][j] = fmaf(vv, x[j], acc[k][j]);
-            }
-          }
+          const int2 q = stage[s + sub];
+          gather(q.x, __int_as_float(q.y));
         }
       }
     }
@@ -127,20 +147,23 @@ __device__ __forceinline__ int live_vectors(int tile0, int l, int f_eff) {
   return min(NV, (f_eff - first + LPN * VEC - 1) / (LPN * VEC));
 }
 
+constexpr int kMaxRowsPerBlock = 8;
+
 template <int VEC, int LPN, int NV>
-__global__ void __launch_bounds__(256) spmm_warp_rows_kernel(const int* __restrict__ rowptr, const int* __restrict__ col,
-                                                             const float* __restrict__ val, int n,
-                                                             const float* __restrict__ B, int64_t ldb,
-                                                             float* __restrict__ C, int64_t ldc, int f_eff, float beta,
-                                                             const int* __restrict__ plan) {
-  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (row >= n) return;
+__global__ void __launch_bounds__(kMaxRowsPerBlock * 32) spmm_warp_rows_kernel(
+    const int* __restrict__ rowptr, const int* __restrict__ col, const float* __restrict__ val, int n,
+    const float* __restrict__ B, int ldb, float* __restrict__ C, int ldc, int f_eff, float beta,
+    const int* __restrict__ plan, int min_threshold) {
+  __shared__ __align__(16) int2 stage[kMaxRowsPerBlock][32];
+  const int warp = threadIdx.x >> 5;
+  const int row = blockIdx.x * (blockDim.x >> 5) + warp;
+  if (row >= n) return;                      // whole warps leave together; nothing below is block-wide
   const int lane = threadIdx.x & 31;
   const int l = lane % LPN;
   const int tile0 = blockIdx.y * (LPN * VEC * NV);
   const int start = __ldg(rowptr + row);
   const int end = __ldg(rowptr + row + 1);
-  const int long_threshold = plan ? __ldg(plan + 2) : INT_MAX;
+  const int long_threshold = plan ? max(__ldg(plan + 2), min_threshold) : INT_MAX;
   if (end - start > long_threshold) return;  // a hub row: the block-per-row kernel owns it
   const int nvalid = live_vectors<VEC, LPN, NV>(tile0, l, f_eff);
 
@@ -150,7 +173,7 @@ __global__ void __launch_bounds__(256) spmm_warp_rows_kernel(const int* __restri
 #pragma unroll
     for (int j = 0; j < VEC; ++j) acc[k][j] = 0.f;
 
-  accumulate_range<VEC, LPN, NV>(col, val, start, end, B + tile0 + l * VEC, ldb, nvalid, lane, acc);
+  accumulate_range<VEC, LPN, NV>(col, val, start, end, B + tile0 + l * VEC, ldb, nvalid, lane, stage[warp], acc);
 
   if (lane < LPN) {
     float* cp = C + static_cast<int64_t>(row) * ldc + tile0 + l * VEC;
@@ -170,14 +193,14 @@ __global__ void __launch_bounds__(256) spmm_warp_rows_kernel(const int* __restri
 }
 
 template <int VEC, int LPN, int NV>
-__global__ void __launch_bounds__(kLongWarps * 32) spmm_block_rows_kernel(const int* __restrict__ rowptr,
-                                                                          const int* __restrict__ col,
-                                                                          const float* __restrict__ val,
-                                                                          const float* __restrict__ B, int64_t ldb,
-                                                                          float* __restrict__ C, int64_t ldc, int f_eff,
-                                                                          float beta, const int* __restrict__ plan) {
+__global__ void __launch_bounds__(kLongWarps * 32) spmm_block_rows_kernel(
+    const int* __restrict__ rowptr, const int* __restrict__ col, const float* __restrict__ val,
+    const float* __restrict__ B, int ldb, float* __restrict__ C, int ldc, int f_eff, float beta,
+    const int* __restrict__ plan, int min_threshold) {
   constexpr int TILE = LPN * VEC * NV;
   __shared__ float part[kLongWarps][TILE];
+  __shared__ __align__(16) int2 stage[kLongWarps][32];
+  const int long_threshold = max(__ldg(plan + 2), min_threshold);
   const int count = min(__ldg(plan + 1), __ldg(plan + 3));
   const int* list = plan + kPlanHeaderInts;
   const int lane = threadIdx.x & 31;
@@ -190,6 +213,7 @@ __global__ void __launch_bounds__(kLongWarps * 32) spmm_block_rows_kernel(const 
     const int row = __ldg(list + item);
     const int start = __ldg(rowptr + row);
     const int end = __ldg(rowptr + row + 1);
+    if (end - start <= long_threshold) continue;   // listed, but short enough for the warp-per-row pass at this width
     const int per = (((end - start) + kLongWarps - 1) / kLongWarps + 31) & ~31;
     const int ws = min(end, start + warp * per);
     const int we = min(end, ws + per);
@@ -199,7 +223,7 @@ __global__ void __launch_bounds__(kLongWarps * 32) spmm_block_rows_kernel(const 
     for (int k = 0; k < NV; ++k)
 #pragma unroll
       for (int j = 0; j < VEC; ++j) acc[k][j] = 0.f;
-    accumulate_range<VEC, LPN, NV>(col, val, ws, we, B + tile0 + l * VEC, ldb, nvalid, lane, acc);
+    accumulate_range<VEC, LPN, NV>(col, val, ws, we, B + tile0 + l * VEC, ldb, nvalid, lane, stage[warp], acc);
 
     if (lane < LPN) {
 #pragma unroll
@@ -223,12 +247,27 @@ __global__ void __launch_bounds__(kLongWarps * 32) spmm_block_rows_kernel(const 
   }
 }
 
-__global__ void spmm_plan_kernel(const int* __restrict__ rowptr, int n, int threshold, int capacity, int* plan) {
+// Appends the rows with lo < nonzeros <= hi to the plan's list.
+__global__ void spmm_plan_kernel(const int* __restrict__ rowptr, int n, int lo, int hi, int capacity, int* plan) {
   const int row = blockIdx.x * blockDim.x + threadIdx.x;
   if (row >= n) return;
-  if (rowptr[row + 1] - rowptr[row] > threshold) {
+  const int len = rowptr[row + 1] - rowptr[row];
+  if (len > lo && len <= hi) {
     const int slot = atomicAdd(plan + 1, 1);
     if (slot < capacity) plan[kPlanHeaderInts + slot] = row;
+  }
+}
+
+// The list is filled longest rows first (four length classes, one pass each): the block-per-row kernel walks it
+// in order, and a 100K-nonzero row that starts last would be the tail of the whole launch.
+static void launch_plan_passes(const int* rowptr, int n, int threshold, int capacity, int* plan, cudaStream_t s) {
+  const int64_t t = threshold;
+  const int64_t cuts[5] = {INT_MAX, 32 * t, 8 * t, 2 * t, t};
+  for (int pass = 0; pass < 4; ++pass) {
+    const int hi = static_cast<int>(cuts[pass] > INT_MAX ? INT_MAX : cuts[pass]);
+    const int lo = static_cast<int>(cuts[pass + 1] > INT_MAX ? INT_MAX : cuts[pass + 1]);
+    if (lo >= hi) continue;
+    spmm_plan_kernel<<<(n + 255) / 256, 256, 0, s>>>(rowptr, n, lo, hi, capacity, plan);
   }
 }
 
@@ -243,20 +282,23 @@ static int plan_capacity(int64_t nnz, int threshold) { return static_cast<int>(n
 
 template <int VEC, int LPN, int NV>
 static int launch_spmm(const int* rowptr, const int* col, const float* val, int n, int m, int64_t nnz, const float* B,
-                       int64_t ldb, float* C, int64_t ldc, int f_eff, float beta, const int* plan,
+                       int64_t ldb64, float* C, int64_t ldc64, int f_eff, float beta, const int* plan,
                        cudaStream_t stream) {
+  const int ldb = static_cast<int>(ldb64), ldc = static_cast<int>(ldc64);   // checked to fit by the entry point
+  (void)m;
   constexpr int TILE = LPN * VEC * NV;
   const int tiles = (f_eff + TILE - 1) / TILE;
+  const int min_threshold = (LPN < 32) ? g_tuning.spmm_long_narrow : 0;
   if (plan) {
     // grid-stride over the listed rows, so any grid size is correct; this one is tight for the
     // current threshold and never below one wave
     const int blocks = max(1, min(plan_capacity(nnz, max(g_tuning.spmm_long, kMinLongThreshold)), 16 * kNumSMs));
     spmm_block_rows_kernel<VEC, LPN, NV><<<dim3(blocks, tiles), kLongWarps * 32, 0, stream>>>(
-        rowptr, col, val, B, ldb, C, ldc, f_eff, beta, plan);
+        rowptr, col, val, B, ldb, C, ldc, f_eff, beta, plan, min_threshold);
   }
   const int rows_per_block = g_tuning.spmm_rpb;
   spmm_warp_rows_kernel<VEC, LPN, NV><<<dim3((n + rows_per_block - 1) / rows_per_block, tiles), rows_per_block * 32, 0,
-                                        stream>>>(rowptr, col, val, n, B, ldb, C, ldc, f_eff, beta, plan);
+                                        stream>>>(rowptr, col, val, n, B, ldb, C, ldc, f_eff, beta, plan, min_threshold);
   return check_launch("cagnet_spmm_csr_f32");
 }
 
@@ -314,6 +356,11 @@ extern "C" int cagnet_set_param(const char* name, int value) {
     g_tuning.spmm_rpb = value;
     return CAGNET_OK;
   }
+  if (!strcmp(name, "spmm_long_narrow")) {
+    if (value < kMinLongThreshold) return fail(CAGNET_E_ARG, "cagnet_set_param: spmm_long_narrow must be >= 256");
+    g_tuning.spmm_long_narrow = value;
+    return CAGNET_OK;
+  }
   if (!strcmp(name, "spmm_long")) {
     if (value < kMinLongThreshold) return fail(CAGNET_E_ARG, "cagnet_set_param: spmm_long must be >= 256");
     g_tuning.spmm_long = value;
@@ -326,6 +373,7 @@ extern "C" int cagnet_get_param(const char* name) {
   if (name && !strcmp(name, "spmm_tile")) return g_tuning.spmm_tile;
   if (name && !strcmp(name, "spmm_rpb")) return g_tuning.spmm_rpb;
   if (name && !strcmp(name, "spmm_long")) return g_tuning.spmm_long;
+  if (name && !strcmp(name, "spmm_long_narrow")) return g_tuning.spmm_long_narrow;
   return -1;
 }
 
@@ -347,7 +395,7 @@ extern "C" int cagnet_spmm_plan_i32(const int32_t* rowptr, int32_t n, int64_t nn
   const int threshold = g_tuning.spmm_long;
   const int capacity = plan_capacity(nnz, threshold);
   spmm_plan_header_kernel<<<1, 1, 0, s>>>(threshold, capacity, static_cast<int*>(plan));
-  if (n > 0) spmm_plan_kernel<<<(n + 255) / 256, 256, 0, s>>>(rowptr, n, threshold, capacity, static_cast<int*>(plan));
+  if (n > 0) launch_plan_passes(rowptr, n, threshold, capacity, static_cast<int*>(plan), s);
   return check_launch("cagnet_spmm_plan_i32");
 }
 
@@ -362,6 +410,8 @@ extern "C" int cagnet_spmm_csr_f32(const int32_t* rowptr, const int32_t* col, co
   if (nnz > INT_MAX) return fail(CAGNET_E_OVERFLOW, "cagnet_spmm_csr_f32: nnz %s%lld exceeds int32", "", nnz);
   if (ldb < f || ldc < f)
     return fail(CAGNET_E_ALIGN, "cagnet_spmm_csr_f32: leading dimension%s (%lld, %lld) smaller than f", "", ldb, ldc);
+  if (ldb > INT_MAX || ldc > INT_MAX)
+    return fail(CAGNET_E_OVERFLOW, "cagnet_spmm_csr_f32: leading dimension%s (%lld, %lld) exceeds int32", "", ldb, ldc);
   if (!B) B = C;  // nnz == 0: never dereferenced
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int* p = static_cast<const int*>(plan);
@@ -443,7 +493,7 @@ extern "C" int cagnet_spmm_csr_f32_noalloc(const int32_t* rowptr, const int32_t*
   const int capacity = min(plan_capacity(nnz, threshold), kStaticPlanRows);
   // the array keeps whatever the previous call left in it: the header kernel resets the row count first
   spmm_plan_header_kernel<<<1, 1, 0, s>>>(threshold, capacity, plan);
-  spmm_plan_kernel<<<(n + 255) / 256, 256, 0, s>>>(rowptr, n, threshold, capacity, plan);
+  launch_plan_passes(rowptr, n, threshold, capacity, plan, s);
   const int lrc = check_launch("cagnet_spmm_csr_f32_noalloc");
   if (lrc != CAGNET_OK) return lrc;
   return cagnet_spmm_csr_f32(rowptr, col, val, n, m, nnz, B, ldb, C, ldc, f, beta, plan, stream);

@@ -186,7 +186,7 @@ class CsrBlock:
             _native.check(_native.lib().cagnet_spmm_plan_i32(self.rowptr.data_ptr(), self.n, self.nnz,
                                                              self.plan.data_ptr(), self.plan.numel(), _stream()),
                           "spmm_plan")
-        LAUNCHES[0] += 2
+        LAUNCHES[0] += 5      # header + four length-class passes
 
     def long_rows(self):
         """Number of rows the plan routes to the block-per-row kernel (synchronises)."""

@@ -44,7 +44,8 @@ const char* cagnet_last_error_string(void);
 
 /* Tuning knobs, for sweeps: "spmm_tile" (vectors per feature tile, 0 = automatic), "spmm_rpb" (rows per thread
  * block of the warp-per-row kernel), "spmm_long" (rows with
- * more nonzeros than this are listed in the plan and processed by a whole thread block).  Host-side global
+ * more nonzeros than this are listed in the plan and processed by a whole thread block), "spmm_long_narrow"
+ * (the same limit as applied by products narrower than 128 columns).  Host-side global
  * state; returns CAGNET_E_ARG for an unknown name or value. */
 int cagnet_set_param(const char* name, int value);
 int cagnet_get_param(const char* name);
@@ -88,8 +89,8 @@ int cagnet_spmm_csr_f32(const int32_t* rowptr, const int32_t* col, const float* 
  * hub-row list is built, on `stream`, in a fixed 256 KB device array that is part of the library (each GPU
  * that loads the library holds it until the process exits), then the multiply runs exactly as
  * cagnet_spmm_csr_f32 does with a plan.  Nothing is allocated or freed, here or in anything it calls.
- *   - Limit: nnz <= cagnet_spmm_noalloc_max_nnz() (65,535 x the hub-row threshold: about 268 M at the default
- *     4096); beyond it the call returns CAGNET_E_WORKSPACE and does nothing.
+ *   - Limit: nnz <= cagnet_spmm_noalloc_max_nnz() (65,535 x the hub-row threshold: about 134 M at the default
+ *     2048); beyond it the call returns CAGNET_E_WORKSPACE and does nothing.
  *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that
  *     device current); make that first call before starting any stream capture.
  *   - All calls share the one array and the array keeps the last call's list: each call resets it first, and

@@ -93,3 +93,44 @@ def test_power_law_graph_epoch_and_linearity():
     colsum = torch.zeros(n, dtype=torch.float64)
     colsum.index_add_(0, A.col.cpu().long(), A.val.cpu().double())
     assert _rel(c1.double().sum(0).cpu(), colsum @ b1.double().cpu()) <= 1e-4
+
+
+@pytest.mark.parametrize("algo,name", [("2d", "train_1d_P1.npz"), ("3d", "train_1d_P1_plain.npz")])
+def test_2d_and_3d_code_paths_on_one_gpu(golden_dir, algo, name):
+    """On a 1 x 1 (x 1) grid the SUMMA schedules degenerate to the single-process model, so the reference's
+    single-rank fixtures apply: the 2D path (distributed log-softmax pieces, accumulate epilogues, transposed
+    products) against the normalised/activated run, the 3D path against the linear unnormalised one."""
+    from cagnet_b200 import dist1d, dist2d, dist3d, graphs
+    from cagnet_b200.backend import CudaBackend
+    d = np.load(os.path.join(golden_dir, name))
+    n, f, mid, classes, epochs, P, c, norm, act = d["cfg"].tolist()
+    edge, x, y, mask = (torch.from_numpy(d[k]) for k in ("edge_index", "x", "y", "mask"))
+    adj = graphs.add_self_loops(edge, n) if norm else edge
+    data = dist1d.Data(y=y, train_mask=mask)
+    if algo == "2d":
+        model = dist2d.Model(dist2d.Runtime(CudaBackend(), bool(act), bool(norm)), 0, 1, x, adj, data, f, classes)
+    else:
+        model = dist3d.Model(dist3d.Runtime(CudaBackend(), bool(act), bool(norm)), 0, 1, x, adj, data, f, classes)
+    model.init_weights(mid)
+    for ep in range(epochs):
+        out = model.train()
+        assert _rel(out.detach(), d[f"r0_ep{ep}_out"]) <= 1e-4, ("activations", ep)
+        assert _rel(model.weight1.grad, d[f"r0_ep{ep}_gw1"]) <= 1e-4, ("gW1", ep)
+        assert _rel(model.weight2.grad, d[f"r0_ep{ep}_gw2"]) <= 1e-4, ("gW2", ep)
+        assert _rel(model.weight1.detach(), d[f"r0_ep{ep}_w1"]) <= 1e-4, ("W1", ep)
+
+
+def test_min_width_order_on_gpu(golden_dir):
+    from cagnet_b200 import dist1d, graphs
+    from cagnet_b200.backend import CudaBackend
+    d = np.load(os.path.join(golden_dir, "train_1d_P1.npz"))
+    n, f, mid, classes, epochs = d["cfg"][:5].tolist()
+    edge, x, y, mask = (torch.from_numpy(d[k]) for k in ("edge_index", "x", "y", "mask"))
+    rt = dist1d.Runtime(CudaBackend(), True, True, order="min_width")
+    model = dist1d.Model(rt, 0, 1, x, graphs.add_self_loops(edge, n), dist1d.Data(y=y, train_mask=mask), f, classes)
+    model.init_weights(mid)
+    for ep in range(epochs):
+        out = model.train()
+        assert _rel(out.detach(), d[f"r0_ep{ep}_out"]) <= 1e-4
+        assert _rel(model.weight1.grad, d[f"r0_ep{ep}_gw1"]) <= 1e-4
+        assert _rel(model.weight2.detach(), d[f"r0_ep{ep}_w2"]) <= 1e-4

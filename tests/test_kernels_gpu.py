@@ -247,3 +247,47 @@ def test_spmm_on_rmat_graph_with_normalised_values():
         C = ops.zeros_padded(n, f, "cuda")
         ops.spmm(A, ops.to_padded(B.cuda()), C, 0.0)
         _close(C, torch.sparse.mm(M64, B.double()))
+
+
+@pytest.mark.parametrize("n,N", [(500, 21), (33, 128), (7, 1)])
+def test_split_log_softmax_pieces(n, N):
+    """The row-wise pieces a process row combines with collectives: here the 'collective' is a sum over two
+    column halves held by one process, checked against the whole-row log-softmax and its gradient."""
+    g = torch.Generator().manual_seed(n)
+    z, gr = 2 * torch.randn(n, N, generator=g), torch.randn(n, N, generator=g)
+    h = max(1, N // 2)
+    parts = [(z[:, :h], gr[:, :h]), (z[:, h:], gr[:, h:])] if N > 1 else [(z, gr)]
+    dev = [(ops.to_padded(a.contiguous().cuda()), ops.to_padded(b.contiguous().cuda())) for a, b in parts]
+    m = torch.stack([ops.row_reduce(a, ops.ROW_MAX) for a, _ in dev]).max(0)[0]
+    s = torch.stack([ops.row_reduce(a, ops.ROW_SUMEXP, m) for a, _ in dev]).sum(0)
+    rs = torch.stack([ops.row_reduce(b, ops.ROW_SUM) for _, b in dev]).sum(0)
+    want = torch.log_softmax(z.double(), dim=1)
+    z64 = z.double().requires_grad_(True)
+    torch.log_softmax(z64, dim=1).backward(gr.double())
+    col = 0
+    for a, b in dev:
+        w = a.size(1)
+        logp = ops.log_softmax_apply(a, m, s)
+        _close(logp, want[:, col:col + w])
+        _close(ops.log_softmax_bwd_apply(logp, b, rs), z64.grad[:, col:col + w])
+        col += w
+
+
+def test_accumulating_products():
+    g = torch.Generator().manual_seed(9)
+    X, W, Z0 = torch.randn(700, 37, generator=g), torch.randn(37, 21, generator=g), torch.randn(700, 21, generator=g)
+    Zd = ops.to_padded(Z0.cuda())
+    ops.gemm_nn(ops.to_padded(X.cuda()), W.cuda(), False, ops.EPI_ACCUMULATE, out=Zd)
+    _close(Zd, Z0.double() + X.double() @ W.double())
+    Wt = torch.randn(21, 37, generator=g)
+    Zd = ops.to_padded(Z0.cuda())
+    ops.gemm_nn(ops.to_padded(X.cuda()), Wt.cuda(), True, ops.EPI_ACCUMULATE, out=Zd)
+    _close(Zd, Z0.double() + X.double() @ Wt.double().t())
+    # a strided slice of a larger weight, as the SUMMA stages pass it
+    big = torch.randn(50, 40, generator=g).cuda()
+    part = big[5:42, 11:32]
+    _close(ops.gemm_nn(ops.to_padded(X.cuda()), part), X.double() @ part.double().cpu())
+    H, G, O0 = torch.randn(900, 13, generator=g), torch.randn(900, 9, generator=g), torch.randn(13, 9, generator=g)
+    Od = O0.cuda().clone()
+    ops.gemm_tn(H.cuda(), G.cuda(), out=Od, accumulate=True)
+    _close(Od, O0.double() + H.double().t() @ G.double())
