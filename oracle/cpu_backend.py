@@ -127,3 +127,90 @@ class CpuBackend:
 
     def synchronize(self):
         pass
+
+
+class PaddedCpuBackend(CpuBackend):
+    """The same checker, but every matrix it hands out uses the product's padded row-major layout
+    (`cagnet_b200.ops.pad_ld`) with NaN in the pad columns, and `wire()` returns the padded buffer as the CUDA
+    backend does.  Run over Gloo it catches what a contiguous CPU tensor hides: a schedule that sends a view of
+    the wrong size, slices a padded matrix as if it were dense, or lets pad columns leak into real ones."""
+    name = "cpu-oracle-padded"
+
+    @staticmethod
+    def _padded_nan(n, f):
+        from cagnet_b200 import ops
+        ld = ops.pad_ld(f)
+        flat = torch.full((max(n * ld, 1),), float("nan"))
+        return ops._alias(flat, 0, (n, f), (ld, 1))
+
+    @classmethod
+    def _to_padded(cls, x):
+        out = cls._padded_nan(x.size(0), x.size(1))
+        out.copy_(x)
+        return out
+
+    @staticmethod
+    def _is_padded(x):
+        from cagnet_b200 import ops
+        if x.dim() != 2 or x.dtype != torch.float32:
+            return False
+        if x.size(0) > 1 and x.stride(0) != ops.pad_ld(x.size(1)):
+            return False
+        if x.size(1) > 1 and x.stride(1) != 1:
+            return False
+        if x.storage_offset() % ops.pad_ld(x.size(1)) != 0:
+            return False
+        try:
+            ops.base_buffer(x)
+        except RuntimeError:
+            return False
+        return True
+
+    def empty(self, n, f):
+        return self._padded_nan(n, f)
+
+    def zeros(self, n, f):
+        z = self._padded_nan(n, f)
+        z.zero_()
+        return z
+
+    def as_matrix(self, x):
+        x = x.detach()
+        return x if self._is_padded(x) else self._to_padded(x.float())
+
+    def wire(self, x):
+        from cagnet_b200 import ops
+        return ops.base_buffer(x)
+
+    def spmm(self, blk, B, C, beta):
+        prod = torch.sparse.mm(blk.mat, B.contiguous())
+        if beta:
+            C.add_(prod)
+        else:
+            C.copy_(prod)
+        return C
+
+    def mm(self, X, W, act="none"):
+        return self._to_padded(super().mm(X.contiguous(), W, act))
+
+    def mm_nt(self, X, W):
+        return self._to_padded(X.contiguous() @ W.t())
+
+    def mm_tn(self, H, G):
+        return H.contiguous().t() @ G.contiguous()
+
+    def act(self, z, act):
+        return self._to_padded(super().act(z.contiguous(), act))
+
+    def act_bwd(self, out, g, act):
+        return self._to_padded(super().act_bwd(out.contiguous(), g.contiguous(), act))
+
+    def log_softmax_apply(self, z, row_max, row_sum):
+        return self._to_padded(super().log_softmax_apply(z.contiguous(), row_max, row_sum))
+
+    def log_softmax_bwd_apply(self, logp, g, row_sum_g):
+        return self._to_padded(super().log_softmax_bwd_apply(logp.contiguous(), g.contiguous(), row_sum_g))
+
+    def nll(self, logp, y, mask, count, cls_lo=0, cls_hi=None):
+        loss, grad = super().nll(logp.contiguous(), y, mask, count, cls_lo, cls_hi)
+        return loss, self._to_padded(grad)

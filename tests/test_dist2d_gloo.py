@@ -8,17 +8,18 @@ import pytest
 from tests.mp_util import run_ranks
 
 
-def _worker(rank, world, case_path, cache_blocks, overlap):
+def _worker(rank, world, case_path, cache_blocks, overlap, padded=False):
     import numpy as np
     import torch
     from cagnet_b200 import dist2d, graphs
-    from oracle.cpu_backend import CpuBackend
+    from oracle.cpu_backend import CpuBackend, PaddedCpuBackend
+    Backend = PaddedCpuBackend if padded else CpuBackend
 
     d = np.load(case_path)
     n, f, mid, classes, epochs = d["cfg"][:5].tolist()
     edge, x, y, mask = (torch.from_numpy(d[k]) for k in ("edge_index", "x", "y", "mask"))
     adj = graphs.add_self_loops(edge, n)
-    rt = dist2d.Runtime(CpuBackend(), True, True, timing=False, overlap=overlap, cache_blocks=cache_blocks)
+    rt = dist2d.Runtime(Backend(), True, True, timing=False, overlap=overlap, cache_blocks=cache_blocks)
     model = dist2d.Model(rt, rank, world, x, adj, dist2d.Data(y=y, train_mask=mask), f, classes)
     model.init_weights(mid)
     out = {}
@@ -32,12 +33,12 @@ def _worker(rank, world, case_path, cache_blocks, overlap):
     return out
 
 
-@pytest.mark.parametrize("cache_blocks,overlap", [(True, True), (False, False)])
-def test_2d_matches_reference_fixture(golden_dir, cache_blocks, overlap):
+@pytest.mark.parametrize("cache_blocks,overlap,padded", [(True, True, False), (False, False, False), (True, True, True)])
+def test_2d_matches_reference_fixture(golden_dir, cache_blocks, overlap, padded):
     path = os.path.join(golden_dir, "train_2d_P4.npz")
     d = np.load(path)
     epochs, P = int(d["cfg"][4]), int(d["cfg"][5])
-    results = run_ranks(P, _worker, path, cache_blocks, overlap)
+    results = run_ranks(P, _worker, path, cache_blocks, overlap, padded)
     for rank, res in enumerate(results):
         for ep in range(epochs):
             for key in ("out", "gw1", "gw2", "w1", "w2"):

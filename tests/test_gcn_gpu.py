@@ -99,7 +99,9 @@ def test_power_law_graph_epoch_and_linearity():
 def test_2d_and_3d_code_paths_on_one_gpu(golden_dir, algo, name):
     """On a 1 x 1 (x 1) grid the SUMMA schedules degenerate to the single-process model, so the reference's
     single-rank fixtures apply: the 2D path (distributed log-softmax pieces, accumulate epilogues, transposed
-    products) against the normalised/activated run, the 3D path against the linear unnormalised one."""
+    products) against the normalised/activated run, the 3D path against the linear unnormalised one.
+    The 2D/3D scripts pair the p-th TRAIN label with local row p (a quirk the 1D script does not have), so the
+    quirk is switched off here; with it on, the 2D/3D fixtures of tests/test_multi_gpu.py apply."""
     from cagnet_b200 import dist1d, dist2d, dist3d, graphs
     from cagnet_b200.backend import CudaBackend
     d = np.load(os.path.join(golden_dir, name))
@@ -108,9 +110,9 @@ def test_2d_and_3d_code_paths_on_one_gpu(golden_dir, algo, name):
     adj = graphs.add_self_loops(edge, n) if norm else edge
     data = dist1d.Data(y=y, train_mask=mask)
     if algo == "2d":
-        model = dist2d.Model(dist2d.Runtime(CudaBackend(), bool(act), bool(norm)), 0, 1, x, adj, data, f, classes)
+        model = dist2d.Model(dist2d.Runtime(CudaBackend(), bool(act), bool(norm), reference_label_alignment=False), 0, 1, x, adj, data, f, classes)
     else:
-        model = dist3d.Model(dist3d.Runtime(CudaBackend(), bool(act), bool(norm)), 0, 1, x, adj, data, f, classes)
+        model = dist3d.Model(dist3d.Runtime(CudaBackend(), bool(act), bool(norm), reference_label_alignment=False), 0, 1, x, adj, data, f, classes)
     model.init_weights(mid)
     for ep in range(epochs):
         out = model.train()
