@@ -374,8 +374,8 @@ def main():
     ap.add_argument("--collective", default="all_gather", choices=["all_gather", "broadcast"],
                     help="how H blocks travel in a 1D sparse product: one all-gather per launch group, or one "
                          "broadcast per source rank as the reference issues them")
-    ap.add_argument("--stage-groups", type=int, default=2,
-                    help="launch groups per distributed sparse product (0 = one per stage, as the reference)")
+    ap.add_argument("--stage-groups", type=int, default=-1,
+                    help="launch groups per distributed sparse product (0 = one per stage, as the reference; -1 = automatic)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -38,7 +38,7 @@ class Runtime:
     """Per-process settings: what the reference keeps in module globals (gcn_distr.py:53-64)."""
 
     def __init__(self, backend, activations=True, normalization=True, replication=1, timing=False, overlap=True,
-                 categories=None, order="reference", stage_groups=2, collective="all_gather"):
+                 categories=None, order="reference", stage_groups=-1, collective="all_gather"):
         if order not in ("reference", "min_width"):
             raise ValueError("order must be 'reference' or 'min_width'")
         if collective not in ("all_gather", "broadcast"):
@@ -47,7 +47,8 @@ class Runtime:
         # reference issues them; "all_gather" = the same bytes in one collective per launch group
         self.collective = collective
         self.order = order
-        self.stage_groups = stage_groups     # launch groups per sparse product; 0 = one per stage, as the reference
+        # launch groups per sparse product: 0 = one per stage, as the reference; -1 = automatic (see Model)
+        self.stage_groups = stage_groups
         self.backend = backend
         self.activations = bool(activations)
         self.normalization = bool(normalization)
@@ -63,10 +64,6 @@ def act_name(func):
     if func is F.log_softmax or func == ACT_LOG_SOFTMAX:
         return ACT_LOG_SOFTMAX
     return ACT_NONE
-
-
-def _group_size(group):
-    return dist.get_world_size(group) if dist.is_available() and dist.is_initialized() else 1
 
 
 # ------------------------------------------------------------------------------------------ schedule
@@ -353,10 +350,14 @@ class Model:
         inputs_loc, blocks = partition.oned_partition(rank, size, inputs, adj_matrix, rt.normalization, c)
         self.inputs_loc = be.as_matrix(inputs_loc)
         n_per_proc = int(math.ceil(float(node_count) / (size / c)))
+        # automatic launch groups: two (communication of the second under the multiply of the first) up to 4
+        # ranks, one beyond -- the per-rank multiply shrinks as 1/P while the cost of a launch does not, and on the
+        # 233K-vertex benchmark graph the crossover lies between 4 and 8 ranks (6.8 ms against 7.6 ms per epoch at 8)
+        groups = rt.stage_groups if rt.stage_groups >= 0 else (2 if size <= 4 else 1)
         if c == 1 and size > 1 and rt.collective == "all_gather":
-            self.am_pbyp = GatherPlan(be, blocks, rank, size, n_per_proc, rt.stage_groups)
+            self.am_pbyp = GatherPlan(be, blocks, rank, size, n_per_proc, groups)
         else:
-            self.am_pbyp = StagePlan(be, blocks, rank, size, c, rt.stage_groups)
+            self.am_pbyp = StagePlan(be, blocks, rank, size, c, groups)
         rank_c = rank // c
         lo, hi = rank_c * n_per_proc, min(node_count, (rank_c + 1) * n_per_proc)
         dev = self.inputs_loc.device
@@ -364,20 +365,44 @@ class Model:
         self.datay_rank = data.y[lo:hi].long().to(dev)
         self.train_count = int(self.rank_train_mask.sum())
 
-    def init_weights(self, mid_layer):
-        """torch.manual_seed(0); rand on the CPU, then moved (gcn_distr.py:550-560)."""
+    def init_weights(self, mid_layer, capturable=False):
+        """torch.manual_seed(0); rand on the CPU, then moved (gcn_distr.py:550-560).  `capturable` keeps Adam's
+        step count on the device so that an epoch can be recorded into a CUDA graph (see `capture`)."""
         torch.manual_seed(0)
         dev = self.inputs_loc.device
         w1 = torch.rand(self.features, mid_layer, requires_grad=True).to(dev)
         w2 = torch.rand(mid_layer, self.classes, requires_grad=True).to(dev)
         self.weight1 = torch.nn.Parameter(w1.detach())
         self.weight2 = torch.nn.Parameter(w2.detach())
-        self.optimizer = torch.optim.Adam([self.weight1, self.weight2], lr=0.01)
+        self.optimizer = torch.optim.Adam([self.weight1, self.weight2], lr=0.01, capturable=bool(capturable))
+        self._graph = self._graph_outputs = None
         return self.weight1, self.weight2
 
-    def train(self):
+    def _train_eager(self):
         return train(self.inputs_loc, self.weight1, self.weight2, None, self.am_pbyp, self.optimizer, self,
                      self.rank, self.size, self.group, self.row_groups, self.col_groups, self.rt)
+
+    def train(self):
+        if getattr(self, "_graph", None) is not None:
+            self._graph.replay()
+            return self._graph_outputs
+        return self._train_eager()
+
+    def capture(self):
+        """Record one whole epoch (both layers, loss, backward, collectives, Adam) into a CUDA graph; `train()`
+        replays it from then on.  An epoch is ~30 launches of this library plus the optimizer's and NCCL's; once
+        the graph is split over 8 GPUs those launches cost more host time than the kernels take.  Call after at
+        least one eager epoch (communicators, Adam state and block caches must exist) with weights created by
+        `init_weights(..., capturable=True)`; the features, labels and mask are read from the tensors the model
+        holds at capture time, so new data has to be copied INTO them.  Capturing does not execute an epoch."""
+        if self.rt.timers.enabled:
+            raise RuntimeError("cagnet_b200: an epoch cannot be captured with --timing=True (it synchronises)")
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+            outputs = self._train_eager()
+        self._graph, self._graph_outputs = graph, outputs
+        return graph
 
 
 def train(inputs, weight1, weight2, adj_matrix, am_partitions, optimizer, model, rank, size, group, row_groups,

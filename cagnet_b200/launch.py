@@ -40,7 +40,8 @@ def parse_args(algorithm, argv=None):
                    help="min_width: run every sparse product at the narrower of a layer's two widths")
     p.add_argument("--collective", type=str, default="all_gather", choices=["all_gather", "broadcast"],
                    help="1D: move H blocks with one all-gather per launch group, or one broadcast per source rank")
-    p.add_argument("--stagegroups", type=int, default=2, help="launch groups per sparse product (0 = one per stage)")
+    p.add_argument("--stagegroups", type=int, default=-1,
+                   help="launch groups per sparse product (0 = one per stage, -1 = automatic)")
     args = p.parse_args(argv)
     print(args)
     missing = [k for k in ("epochs", "graphname", "timing", "midlayer", "runcount") if getattr(args, k) is None]
