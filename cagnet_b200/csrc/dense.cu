@@ -37,39 +37,56 @@ __global__ void __launch_bounds__(256) gemm_nn_kernel(const float* __restrict__ 
 #pragma unroll
     for (int t = 0; t < TN; ++t) acc[i][t] = 0.f;
 
-  for (int k0 = 0; k0 < K; k0 += kBK) {
-    // X tile: 128 rows x 32 k, read row-contiguous, stored k-major
-    {
-      const int kk = (tid & 7) * 4;
+  // The X tile of step k+1 is fetched into registers while step k is being multiplied, so the kernel waits for
+  // HBM once per tile instead of once per tile and synchronisation.
+  constexpr int WPT = (kBK * NT + 255) / 256;     // W elements per thread and step
+  const int kk = (tid & 7) * 4;
+  float xv[4][4];
+  float wv[WPT];
+
+  auto fetch = [&](int k0) {
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int r = (tid >> 3) + 32 * i;
-        const int64_t gr = row0 + r;
-        float v[4] = {0.f, 0.f, 0.f, 0.f};
-        if (gr < n) {
-          const float* xp = X + gr * ldx + k0 + kk;
-          if (x_vec4 && k0 + kk + 3 < K) {
-            const float4 t4 = __ldg(reinterpret_cast<const float4*>(xp));
-            v[0] = t4.x; v[1] = t4.y; v[2] = t4.z; v[3] = t4.w;
-          } else {
+    for (int i = 0; i < 4; ++i) {
+      const int64_t gr = row0 + (tid >> 3) + 32 * i;
 #pragma unroll
-            for (int j = 0; j < 4; ++j)
-              if (k0 + kk + j < K) v[j] = __ldg(xp + j);
-          }
+      for (int j = 0; j < 4; ++j) xv[i][j] = 0.f;
+      if (gr < n) {
+        const float* xp = X + gr * ldx + k0 + kk;
+        if (x_vec4 && k0 + kk + 3 < K) {
+          const float4 t4 = __ldg(reinterpret_cast<const float4*>(xp));
+          xv[i][0] = t4.x; xv[i][1] = t4.y; xv[i][2] = t4.z; xv[i][3] = t4.w;
+        } else {
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            if (k0 + kk + j < K) xv[i][j] = __ldg(xp + j);
         }
-#pragma unroll
-        for (int j = 0; j < 4; ++j) Xs[kk + j][r] = v[j];
       }
     }
-    // W tile: 32 k x NT columns
-    for (int idx = tid; idx < kBK * NT; idx += 256) {
+#pragma unroll
+    for (int u = 0; u < WPT; ++u) {
+      const int idx = tid + 256 * u;
       const int k = idx / NT, j = idx % NT;
       float w = 0.f;
-      if (k0 + k < K && n0 + j < N)
+      if (idx < kBK * NT && k0 + k < K && n0 + j < N)
         w = transW ? __ldg(W + static_cast<int64_t>(n0 + j) * ldw + k0 + k) : __ldg(W + static_cast<int64_t>(k0 + k) * ldw + n0 + j);
-      Ws[k][j] = w;
+      wv[u] = w;
+    }
+  };
+
+  fetch(0);
+  for (int k0 = 0; k0 < K; k0 += kBK) {
+    // X tile: 128 rows x 32 k, read row-contiguous, stored k-major; W tile: 32 k x NT columns
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) Xs[kk + j][(tid >> 3) + 32 * i] = xv[i][j];
+#pragma unroll
+    for (int u = 0; u < WPT; ++u) {
+      const int idx = tid + 256 * u;
+      if (idx < kBK * NT) Ws[idx / NT][idx % NT] = wv[u];
     }
     __syncthreads();
+    if (k0 + kBK < K) fetch(k0 + kBK);
 #pragma unroll 8
     for (int k = 0; k < kBK; ++k) {
       float x[4], w[TN];
@@ -149,16 +166,29 @@ __global__ void __launch_bounds__(256) gemm_tn_partial_kernel(const float* __res
 #pragma unroll
     for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
 
-  for (int64_t r0 = r_begin; r0 < r_end; r0 += kTnRB) {
-    for (int idx = tid; idx < kTnRB * kTnKT; idx += 256) {
+  // 32 rows of H (64 columns) and G (up to 64 columns) per step: 8 + 8 values per thread, fetched into registers
+  // one step ahead of the multiply.
+  float hv[8], gv[8];
+  auto fetch = [&](int64_t r0) {
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int idx = tid + 256 * u;
       const int r = idx / kTnKT, k = idx % kTnKT;
-      Hs[r][k] = (r0 + r < r_end && k0 + k < K) ? __ldg(H + (r0 + r) * ldh + k0 + k) : 0.f;
+      hv[u] = (r0 + r < r_end && k0 + k < K) ? __ldg(H + (r0 + r) * ldh + k0 + k) : 0.f;
+      const int j = idx % kTnNT;
+      gv[u] = (r0 + r < r_end && j < nt) ? __ldg(G + (r0 + r) * ldg + n0 + j) : 0.f;
     }
-    for (int idx = tid; idx < kTnRB * kTnNT; idx += 256) {
-      const int r = idx / kTnNT, j = idx % kTnNT;
-      Gs[r][j] = (r0 + r < r_end && j < nt) ? __ldg(G + (r0 + r) * ldg + n0 + j) : 0.f;
+  };
+  if (r_begin < r_end) fetch(r_begin);
+  for (int64_t r0 = r_begin; r0 < r_end; r0 += kTnRB) {
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int idx = tid + 256 * u;
+      Hs[idx / kTnKT][idx % kTnKT] = hv[u];
+      Gs[idx / kTnNT][idx % kTnNT] = gv[u];
     }
     __syncthreads();
+    if (r0 + kTnRB < r_end) fetch(r0 + kTnRB);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const int u = tid + 256 * i;
