@@ -390,13 +390,16 @@ class Model:
 
     def capture(self):
         """Record one whole epoch (both layers, loss, backward, collectives, Adam) into a CUDA graph; `train()`
-        replays it from then on.  An epoch is ~30 launches of this library plus the optimizer's and NCCL's; once
-        the graph is split over 8 GPUs those launches cost more host time than the kernels take.  Call after at
+        replays it from then on (single process only).  An epoch is ~30 launches of this library plus the
+        optimizer's; replaying them as one graph takes the host out of the loop.  Call after at
         least one eager epoch (communicators, Adam state and block caches must exist) with weights created by
         `init_weights(..., capturable=True)`; the features, labels and mask are read from the tensors the model
         holds at capture time, so new data has to be copied INTO them.  Capturing does not execute an epoch."""
         if self.rt.timers.enabled:
             raise RuntimeError("cagnet_b200: an epoch cannot be captured with --timing=True (it synchronises)")
+        if self.size > 1 and dist.is_initialized():
+            # recording the NCCL calls of an epoch did not return on 2 GPUs with this torch / NCCL pair
+            raise RuntimeError("cagnet_b200: epoch capture is single-process only; multi-rank epochs run eagerly")
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, capture_error_mode="thread_local"):

@@ -136,3 +136,24 @@ def test_min_width_order_on_gpu(golden_dir):
         assert _rel(out.detach(), d[f"r0_ep{ep}_out"]) <= 1e-4
         assert _rel(model.weight1.grad, d[f"r0_ep{ep}_gw1"]) <= 1e-4
         assert _rel(model.weight2.detach(), d[f"r0_ep{ep}_w2"]) <= 1e-4
+
+
+def test_captured_epoch_replays_to_the_same_numbers(golden_dir):
+    """One eager epoch, then the epoch recorded into a CUDA graph and replayed: the reference fixture still holds."""
+    from cagnet_b200 import dist1d, graphs
+    from cagnet_b200.backend import CudaBackend
+    d = np.load(os.path.join(golden_dir, "train_1d_P1.npz"))
+    n, f, mid, classes, epochs = d["cfg"][:5].tolist()
+    edge, x, y, mask = (torch.from_numpy(d[k]) for k in ("edge_index", "x", "y", "mask"))
+    model = dist1d.Model(dist1d.Runtime(CudaBackend(), True, True), 0, 1, x, graphs.add_self_loops(edge, n),
+                         dist1d.Data(y=y, train_mask=mask), f, classes)
+    model.init_weights(mid, capturable=True)
+    out = model.train()
+    assert _rel(out.detach(), d["r0_ep0_out"]) <= 1e-4
+    model.capture()
+    for ep in range(1, epochs):
+        out = model.train()
+        torch.cuda.synchronize()
+        assert _rel(out.detach(), d[f"r0_ep{ep}_out"]) <= 1e-4, ep
+        assert _rel(model.weight1.detach(), d[f"r0_ep{ep}_w1"]) <= 1e-4, ep
+        assert _rel(model.weight2.grad, d[f"r0_ep{ep}_gw2"]) <= 1e-4, ep
