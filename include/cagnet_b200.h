@@ -42,11 +42,11 @@ enum {
 int cagnet_version(void);
 const char* cagnet_last_error_string(void);
 
-/* Tuning knobs, for sweeps: "spmm_tile" (vectors per feature tile, 0 = automatic), "spmm_rpb" (rows per thread
- * block of the warp-per-row kernel), "spmm_long" (rows with
- * more nonzeros than this are listed in the plan and processed by a whole thread block), "spmm_long_narrow"
- * (the same limit as applied by products narrower than 128 columns).  Host-side global
- * state; returns CAGNET_E_ARG for an unknown name or value. */
+/* Tuning knobs, for sweeps: "spmm_tile" (vectors per feature tile; 0 = automatic, which also picks the
+ * two-vectors-per-lane mapping for products of 5..16 vectors), "spmm_rpb" (rows per thread block of the
+ * warp-per-row kernel), "spmm_long" (rows with more nonzeros than this are listed in the plan and processed by a
+ * whole thread block), "spmm_long_narrow" (a lower bound on that limit for products narrower than 128 columns;
+ * equal to "spmm_long" by default).  Host-side global state; returns CAGNET_E_ARG for an unknown name or value. */
 int cagnet_set_param(const char* name, int value);
 int cagnet_get_param(const char* name);
 
