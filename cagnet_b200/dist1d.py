@@ -383,10 +383,13 @@ class Model:
                      self.rank, self.size, self.group, self.row_groups, self.col_groups, self.rt)
 
     def train(self):
+        """One epoch; returns this rank's output rows, detached.  (A caller that kept attached outputs of an eager
+        epoch would keep that epoch's autograd graph alive, and with it the weights' gradient accumulators, which
+        remember the stream they were created under -- a later `capture()` on its own stream then fails.)"""
         if getattr(self, "_graph", None) is not None:
             self._graph.replay()
             return self._graph_outputs
-        return self._train_eager()
+        return self._train_eager().detach()
 
     def capture(self):
         """Record one whole epoch (both layers, loss, backward, collectives, Adam) into a CUDA graph; `train()`
@@ -403,7 +406,7 @@ class Model:
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, capture_error_mode="thread_local"):
-            outputs = self._train_eager()
+            outputs = self._train_eager().detach()
         self._graph, self._graph_outputs = graph, outputs
         return graph
 

@@ -21,7 +21,9 @@ def launch_count():
 
 
 def _stream():
-    return torch.cuda.current_stream().cuda_stream
+    """Raw handle of torch's current stream on the current device (the direct binding: building a
+    torch.cuda.Stream object per launch costs more host time than the launch itself)."""
+    return torch._C._cuda_getCurrentRawStream(torch._C._cuda_getDevice())
 
 
 class _NoSwitch:
@@ -37,7 +39,7 @@ _NO_SWITCH = _NoSwitch()
 
 def _on(device):
     """Context that makes `device` current for a launch; free when it already is (the common case)."""
-    if device.index is None or device.index == torch.cuda.current_device():
+    if device.index is None or device.index == torch._C._cuda_getDevice():
         return _NO_SWITCH
     return torch.cuda.device(device)
 
