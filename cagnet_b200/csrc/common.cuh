@@ -26,7 +26,7 @@ inline int check_launch(const char* what) {
   return CAGNET_OK;
 }
 
-inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
+__host__ __device__ inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
 
 constexpr int kNumSMs = 148;  // B200
 

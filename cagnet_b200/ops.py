@@ -5,6 +5,8 @@ Mirrors the reference's native operator surface (`sparse_coo_tensor_cpp.spmm_gpu
 and adds the cached-CSR form the GCN layers use.  PyTorch is only the owner of device memory and
 streams here; every computation is a kernel of `libcagnet_b200.so`.  CPU tensors are rejected.
 """
+import os
+
 import torch
 
 from . import _native
@@ -125,6 +127,35 @@ def _row_major(t):
     return t.dim() == 2 and (t.size(1) <= 1 or t.stride(1) == 1) and (t.size(0) <= 1 or t.stride(0) >= t.size(1))
 
 
+# Dense-core extraction (see CsrBlock.extract_core).  "density": a rectangle of hub rows x hub columns is worth
+# multiplying densely when more than this share of its cells are nonzeros (gathering one 2.4 KB row of B per
+# nonzero costs about five dense cells at width 602); "step": side lengths tried are multiples of this;
+# "max_side" / "max_bytes": limits of the rectangle; "min_share": the rectangle must save at least this share of
+# the block's nonzero-gathers to be cut out; "min_width": products narrower than this keep using the full CSR
+# block (they are bound per nonzero, not per byte, and a 128-column dense tile would be mostly padding).
+CORE = {"enabled": os.environ.get("CAGNET_DENSE_CORE", "1") != "0", "density": 0.2, "step": 1024, "max_side": 16384,
+        "max_bytes": 2 << 30, "min_share": 0.03, "min_width": 128}
+
+
+def configure_core(**kw):
+    """Change dense-core settings for blocks planned from now on; returns the previous settings."""
+    old = dict(CORE)
+    for k, v in kw.items():
+        if k not in CORE:
+            raise KeyError(k)
+        CORE[k] = v
+    return old
+
+
+def _top_by_degree(deg, limit):
+    """The `limit` highest-degree indices (ties by index, so the choice is reproducible) and, for every index, its
+    position in that list (`limit` for the ones left out)."""
+    order = torch.argsort(deg, descending=True, stable=True)[:limit]
+    rank = torch.full((deg.numel(),), limit, dtype=torch.int64, device=deg.device)
+    rank[order] = torch.arange(order.numel(), device=deg.device)
+    return order, rank
+
+
 # ------------------------------------------------------------------------------------------ sparse
 def coo2csr(rows, n):
     """rowptr[i] = #{e : rows[e] < i} for sorted int32 row indices on the device (int32, n + 1 entries)."""
@@ -148,6 +179,7 @@ class CsrBlock:
     def __init__(self, rowptr, col, val, n, m, plan=None):
         self.rowptr, self.col, self.val, self.n, self.m, self.plan = rowptr, col, val, int(n), int(m), plan
         self.nnz = int(val.numel())
+        self.core = self.rest = None      # dense hub-by-hub rectangle and the CSR block of everything else
 
     @staticmethod
     def from_coo(rows, cols, vals, n, m, validate=True, plan=True):
@@ -181,7 +213,8 @@ class CsrBlock:
                       5: "row index out of range"}.get(code, "?")
             raise RuntimeError("cagnet_b200: malformed sparse block: " + reason)
 
-    def build_plan(self):
+    def build_plan(self, core=True):
+        """Hub-row list for the SpMM kernels and, with `core`, the dense-core split for wide products."""
         nbytes = _native.lib().cagnet_spmm_plan_bytes(self.n, self.nnz)
         self.plan = torch.empty((nbytes + 15) // 16 * 16, dtype=torch.uint8, device=self.val.device)
         with _on(self.val.device):
@@ -189,6 +222,58 @@ class CsrBlock:
                                                              self.plan.data_ptr(), self.plan.numel(), _stream()),
                           "spmm_plan")
         LAUNCHES[0] += 5      # header + four length-class passes
+        if core:
+            self.extract_core()
+
+    def extract_core(self):
+        """Cut the dense core out of a power-law block.
+
+        Rows and columns are ranked by degree; among the rectangles (top r rows) x (top c columns), r and c
+        multiples of CORE["step"], the one with the largest `nonzeros inside - density * cells` is taken if that
+        figure is worth it.  Its entries become a dense r x c fp32 matrix (`self.core`, with the row and column
+        lists) that `spmm` multiplies with cagnet_core_gemm_f32; all other entries form `self.rest`, a CSR block
+        with its own hub-row plan.  The full block stays as it is for narrow products.  Runs once per block, with
+        torch index kernels on the block's device; the choice depends only on the block (ties broken by index)."""
+        cfg = CORE
+        step = int(cfg["step"])
+        if not cfg["enabled"] or self.nnz == 0 or step <= 0:
+            return
+        gr, gc = min(cfg["max_side"], self.n) // step, min(cfg["max_side"], self.m) // step
+        if gr == 0 or gc == 0:
+            return
+        dev = self.val.device
+        rowptr = self.rowptr.long()
+        deg_r = rowptr[1:] - rowptr[:-1]
+        col = self.col.long()
+        deg_c = torch.bincount(col, minlength=self.m)
+        order_r, rank_r = _top_by_degree(deg_r, gr * step)
+        order_c, rank_c = _top_by_degree(deg_c, gc * step)
+        row_of = torch.repeat_interleave(torch.arange(self.n, device=dev), deg_r)
+        er, ec = rank_r[row_of], rank_c[col]
+        inside = (er < gr * step) & (ec < gc * step)
+        hist = torch.bincount((er[inside] // step) * gc + ec[inside] // step, minlength=gr * gc).view(gr, gc)
+        inside_count = hist.cumsum(0).cumsum(1).double()
+        side_r = torch.arange(1, gr + 1, device=dev, dtype=torch.float64) * step
+        side_c = torch.arange(1, gc + 1, device=dev, dtype=torch.float64) * step
+        cells = side_r[:, None] * side_c[None, :]
+        gain = inside_count - float(cfg["density"]) * cells
+        gain[cells * 4 > float(cfg["max_bytes"])] = float("-inf")
+        best = int(torch.argmax(gain))
+        i, j = divmod(best, gc)
+        if not float(gain[i, j]) >= float(cfg["min_share"]) * self.nnz:
+            return
+        r, c = (i + 1) * step, (j + 1) * step
+        in_core = (er < r) & (ec < c)
+        dense = torch.zeros(r, c, dtype=torch.float32, device=dev)
+        dense.index_put_((er[in_core], ec[in_core]), self.val[in_core], accumulate=True)
+        keep = ~in_core
+        kept = deg_r - torch.bincount(row_of[in_core], minlength=self.n)
+        rest_rowptr = torch.zeros(self.n + 1, dtype=torch.int32, device=dev)
+        rest_rowptr[1:] = torch.cumsum(kept, 0).int()
+        rest = CsrBlock(rest_rowptr, self.col[keep].contiguous(), self.val[keep].contiguous(), self.n, self.m)
+        rest.build_plan(core=False)
+        self.rest = rest
+        self.core = (dense, order_r[:r].int().contiguous(), order_c[:c].int().contiguous())
 
     def long_rows(self):
         """Number of rows the plan routes to the block-per-row kernel (synchronises)."""
@@ -208,12 +293,25 @@ def spmm(block, B, C, beta=1.0):
                            % (block.n, block.m, tuple(B.shape), tuple(C.shape)))
     if B.device != block.val.device or C.device != block.val.device:
         raise RuntimeError("cagnet_b200: spmm operands on different devices")
+    f = B.size(1)
+    use_core = block.core is not None and f >= CORE["min_width"] and ldb % 4 == 0 and B.data_ptr() % 16 == 0
+    src = block.rest if use_core else block
     with _on(C.device):
         _native.check(_native.lib().cagnet_spmm_csr_f32(
-            block.rowptr.data_ptr(), block.col.data_ptr(), block.val.data_ptr(), block.n, block.m, block.nnz,
-            B.data_ptr(), ldb, C.data_ptr(), ldc, B.size(1), float(beta),
-            None if block.plan is None else block.plan.data_ptr(), _stream()), "spmm")
-    LAUNCHES[0] += 1 if block.plan is None else 2
+            src.rowptr.data_ptr(), src.col.data_ptr(), src.val.data_ptr(), src.n, src.m, src.nnz,
+            B.data_ptr(), ldb, C.data_ptr(), ldc, f, float(beta),
+            None if src.plan is None else src.plan.data_ptr(), _stream()), "spmm")
+        LAUNCHES[0] += 1 if src.plan is None else 2
+        if use_core:
+            dense, core_rows, core_cols = block.core
+            nbytes = _native.lib().cagnet_core_gemm_workspace_bytes(dense.size(0), dense.size(1), f)
+            ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=C.device)
+            _native.check(_native.lib().cagnet_core_gemm_f32(
+                dense.data_ptr(), dense.stride(0), core_rows.data_ptr(), dense.size(0), core_cols.data_ptr(),
+                dense.size(1), B.data_ptr(), ldb, C.data_ptr(), ldc, f, ws.data_ptr(), ws.numel(), _stream()),
+                "core_gemm")
+            LAUNCHES[0] += 1 if nbytes else 0      # the pass that adds up the k slices
+            LAUNCHES[0] += 1
     return C
 
 
@@ -226,7 +324,7 @@ def spmm_gpu(A_rowindices, A_colindices, A_values, n, m, B, C):
     if n > _INT32_MAX or m > _INT32_MAX:
         raise RuntimeError("cagnet_b200: spmm_gpu block does not fit 32-bit indices")
     block = CsrBlock(coo2csr(A_rowindices, n), A_colindices.contiguous(), A_values.float().contiguous(), n, m)
-    block.build_plan()
+    block.build_plan(core=False)      # a per-call block: the core split only pays when it is reused
     Bc = B if _row_major(B) else B.contiguous()
     if _row_major(C):
         spmm(block, Bc, C, 1.0)

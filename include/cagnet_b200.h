@@ -102,6 +102,21 @@ int cagnet_spmm_csr_f32_noalloc(const int32_t* rowptr, const int32_t* col, const
                                 const float* B, int64_t ldb, float* C, int64_t ldc, int32_t f, float beta,
                                 void* stream);
 
+/* ---- Dense core of a sparse block: C[core_rows[i], 0:f) += sum_j core[i*ld_core + j] * B[core_cols[j], 0:f)
+ * for i < R, j < K.  `core` is the R x K dense fp32 sub-block (zeros where the sparse block has no entry) of
+ * the hub rows `core_rows` (distinct, ascending or not) and hub columns `core_cols` that the host layer cut out
+ * of a CSR block; the remaining entries go through cagnet_spmm_csr_f32, which must be queued first when it
+ * overwrites C (beta = 0).  fp32 FMAs in a fixed order.  B rows 16-byte aligned (ldb % 4 == 0).
+ * The k range is cut into slices whose partial sums pass through `ws` (16-byte aligned, at least
+ * cagnet_core_gemm_workspace_bytes(R, K, f) bytes, which may be 0) and are added up in slice order.
+ * Part of the work cusparseScsrmm2 does at sparse-extension/sparse_coo_tensor.cu:198-226; the reference has
+ * no such split. */
+size_t cagnet_core_gemm_workspace_bytes(int32_t R, int32_t K, int32_t f);
+int cagnet_core_gemm_f32(const float* core, int64_t ld_core, const int32_t* core_rows, int32_t R,
+                         const int32_t* core_cols, int32_t K,
+                         const float* B, int64_t ldb, float* C, int64_t ldc, int32_t f,
+                         void* ws, size_t ws_bytes, void* stream);
+
 /* ---- Z = epilogue(X * W) for a tall X (n x K, ldx) and a small W.
  * transW = 0: W is K x N row-major (ldw);  transW = 1: W is N x K row-major (ldw) and is used
  * transposed (the `mm(ag, weight.t())` form).  aux (n x N, ldaux) is read by CAGNET_EPI_RELU_MASK only.

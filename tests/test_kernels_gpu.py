@@ -291,3 +291,78 @@ def test_accumulating_products():
     Od = O0.cuda().clone()
     ops.gemm_tn(H.cuda(), G.cuda(), out=Od, accumulate=True)
     _close(Od, O0.double() + H.double().t() @ G.double())
+
+
+# ------------------------------------------------------------------------------------------ dense core
+@pytest.mark.parametrize("R,K,f", [(128, 128, 128), (200, 77, 602), (1, 5, 130), (300, 1000, 41), (257, 33, 7),
+                                   (130, 4865, 602), (64, 2049, 100)])
+def test_core_gemm_indexed_rows(R, K, f):
+    """C[rows[i]] += sum_j core[i, j] * B[cols[j]] against fp64, ragged sizes and padded rows included."""
+    g = torch.Generator().manual_seed(R * 7 + K)
+    n, m = R + 50, K + 70
+    core = torch.randn(R, K, generator=g)
+    core[torch.rand(R, K, generator=g) < 0.5] = 0.0
+    rows = torch.randperm(n, generator=g)[:R]
+    cols = torch.randperm(m, generator=g)[:K]
+    B, C0 = torch.randn(m, f, generator=g), torch.randn(n, f, generator=g)
+    want = C0.double()
+    want[rows] += core.double() @ B.double()[cols]
+    Bd, Cd, cored = ops.to_padded(B.cuda()), ops.to_padded(C0.cuda()), core.cuda()
+    rd, cd = rows.int().cuda(), cols.int().cuda()
+    ws = torch.empty(max(_native.lib().cagnet_core_gemm_workspace_bytes(R, K, f), 16), dtype=torch.uint8, device="cuda")
+    _native.check(_native.lib().cagnet_core_gemm_f32(cored.data_ptr(), cored.stride(0), rd.data_ptr(), R, cd.data_ptr(),
+                                                     K, Bd.data_ptr(), Bd.stride(0), Cd.data_ptr(), Cd.stride(0), f,
+                                                     ws.data_ptr(), ws.numel(), None), "core_gemm")
+    torch.cuda.synchronize()
+    _close(Cd, want)
+
+
+def test_core_gemm_rejects_unaligned_rows():
+    z = torch.zeros(8, 7, device="cuda")
+    idx = torch.arange(4, dtype=torch.int32, device="cuda")
+    core = torch.zeros(4, 4, device="cuda")
+    rc = _native.lib().cagnet_core_gemm_f32(core.data_ptr(), 4, idx.data_ptr(), 4, idx.data_ptr(), 4, z.data_ptr(), 7,
+                                            z.data_ptr(), 7, 7, None, 0, None)
+    assert rc == 2 and b"16-byte" in _native.lib().cagnet_last_error_string()
+
+
+@pytest.mark.parametrize("f,beta", [(602, 0.0), (130, 1.0), (128, 0.0)])
+def test_spmm_with_dense_core_matches_oracle(f, beta):
+    """A power-law block whose hub rows x hub columns rectangle is cut out and multiplied densely: same product."""
+    n = 4096
+    edge = graphs.rmat_graph(n, target_nnz=n * 96, seed=5)
+    adj = graphs.add_self_loops(edge, n)
+    _, blocks = PP.oned_partition(0, 1, torch.zeros(n, 1), adj, True)
+    blk = blocks[0]
+    old = ops.configure_core(enabled=True, step=64, max_side=1024, min_share=0.0, density=0.1, min_width=128)
+    try:
+        A = ops.CsrBlock.from_coo(blk.rows, blk.cols, blk.vals, n, n)
+    finally:
+        ops.configure_core(**old)
+    assert A.core is not None, "this graph has a dense core at a 10 % density bar"
+    dense, core_rows, core_cols = A.core
+    assert int((dense != 0).sum()) + A.rest.nnz == A.nnz
+    assert len(set(core_rows.tolist())) == dense.size(0) and len(set(core_cols.tolist())) == dense.size(1)
+    g = torch.Generator().manual_seed(f)
+    B, C0 = torch.randn(n, f, generator=g), torch.randn(n, f, generator=g)
+    want = beta * C0.double() + torch.sparse.mm(_dense64(blk), B.double())
+    C = ops.to_padded(C0.cuda())
+    ops.spmm(A, ops.to_padded(B.cuda()), C, beta)
+    _close(C, want)
+    # narrow products keep using the whole CSR block
+    Bn = torch.randn(n, 16, generator=g)
+    Cn = ops.zeros_padded(n, 16, "cuda")
+    before = ops.launch_count()
+    ops.spmm(A, ops.to_padded(Bn.cuda()), Cn, 0.0)
+    assert ops.launch_count() - before == 2
+    _close(Cn, torch.sparse.mm(_dense64(blk), Bn.double()))
+
+
+def test_no_core_for_uniform_graphs():
+    blk = _random_block(5000, 5000, 20, seed=3)
+    old = ops.configure_core(step=256, max_side=2048)
+    try:
+        A = ops.CsrBlock.from_coo(blk.rows, blk.cols, blk.vals, blk.n_rows, blk.n_cols)
+    finally:
+        ops.configure_core(**old)
+    assert A.core is None and A.rest is None
