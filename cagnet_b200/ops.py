@@ -132,9 +132,11 @@ def _row_major(t):
 # nonzero costs about five dense cells at width 602); "step": side lengths tried are multiples of this;
 # "max_side" / "max_bytes": limits of the rectangle; "min_share": the rectangle must save at least this share of
 # the block's nonzero-gathers to be cut out; "min_width": products narrower than this keep using the full CSR
-# block (they are bound per nonzero, not per byte, and a 128-column dense tile would be mostly padding).
+# block (they are bound per nonzero, not per byte, and a 128-column dense tile would be mostly padding); "rounds":
+# how many rectangles may be cut out one after the other (a second one, 9,216 x 4,096 at 30 % density on the
+# benchmark graph, measured no gain: 13.30 ms against 13.13 ms).
 CORE = {"enabled": os.environ.get("CAGNET_DENSE_CORE", "1") != "0", "density": 0.2, "step": 1024, "max_side": 16384,
-        "max_bytes": 2 << 30, "min_share": 0.03, "min_width": 128}
+        "max_bytes": 2 << 30, "min_share": 0.03, "min_width": 128, "rounds": 1}
 
 
 def configure_core(**kw):
@@ -225,15 +227,17 @@ class CsrBlock:
         if core:
             self.extract_core()
 
-    def extract_core(self):
+    def extract_core(self, depth=0):
         """Cut the dense core out of a power-law block.
 
         Rows and columns are ranked by degree; among the rectangles (top r rows) x (top c columns), r and c
         multiples of CORE["step"], the one with the largest `nonzeros inside - density * cells` is taken if that
         figure is worth it.  Its entries become a dense r x c fp32 matrix (`self.core`, with the row and column
         lists) that `spmm` multiplies with cagnet_core_gemm_f32; all other entries form `self.rest`, a CSR block
-        with its own hub-row plan.  The full block stays as it is for narrow products.  Runs once per block, with
-        torch index kernels on the block's device; the choice depends only on the block (ties broken by index)."""
+        with its own hub-row plan.  The full block stays as it is for narrow products.  `rest` is searched again
+        (the region is L-shaped in a symmetric matrix: hub rows x many columns, then many rows x hub columns), up
+        to CORE["rounds"] rectangles.  Runs once per block, with torch index kernels on the block's device; the
+        choice depends only on the block (ties broken by index)."""
         cfg = CORE
         step = int(cfg["step"])
         if not cfg["enabled"] or self.nnz == 0 or step <= 0:
@@ -272,6 +276,8 @@ class CsrBlock:
         rest_rowptr[1:] = torch.cumsum(kept, 0).int()
         rest = CsrBlock(rest_rowptr, self.col[keep].contiguous(), self.val[keep].contiguous(), self.n, self.m)
         rest.build_plan(core=False)
+        if depth + 1 < int(cfg["rounds"]):
+            rest.extract_core(depth + 1)
         self.rest = rest
         self.core = (dense, order_r[:r].int().contiguous(), order_c[:c].int().contiguous())
 
@@ -295,23 +301,24 @@ def spmm(block, B, C, beta=1.0):
         raise RuntimeError("cagnet_b200: spmm operands on different devices")
     f = B.size(1)
     use_core = block.core is not None and f >= CORE["min_width"] and ldb % 4 == 0 and B.data_ptr() % 16 == 0
-    src = block.rest if use_core else block
+    cores, src = [], block
+    while use_core and src.core is not None:
+        cores.append(src.core)
+        src = src.rest
     with _on(C.device):
         _native.check(_native.lib().cagnet_spmm_csr_f32(
             src.rowptr.data_ptr(), src.col.data_ptr(), src.val.data_ptr(), src.n, src.m, src.nnz,
             B.data_ptr(), ldb, C.data_ptr(), ldc, f, float(beta),
             None if src.plan is None else src.plan.data_ptr(), _stream()), "spmm")
         LAUNCHES[0] += 1 if src.plan is None else 2
-        if use_core:
-            dense, core_rows, core_cols = block.core
+        for dense, core_rows, core_cols in cores:
             nbytes = _native.lib().cagnet_core_gemm_workspace_bytes(dense.size(0), dense.size(1), f)
             ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=C.device)
             _native.check(_native.lib().cagnet_core_gemm_f32(
                 dense.data_ptr(), dense.stride(0), core_rows.data_ptr(), dense.size(0), core_cols.data_ptr(),
                 dense.size(1), B.data_ptr(), ldb, C.data_ptr(), ldc, f, ws.data_ptr(), ws.numel(), _stream()),
                 "core_gemm")
-            LAUNCHES[0] += 1 if nbytes else 0      # the pass that adds up the k slices
-            LAUNCHES[0] += 1
+            LAUNCHES[0] += 2 if nbytes else 1      # the multiply and the pass that adds up its k slices
     return C
 
 

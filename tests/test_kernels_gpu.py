@@ -334,15 +334,20 @@ def test_spmm_with_dense_core_matches_oracle(f, beta):
     adj = graphs.add_self_loops(edge, n)
     _, blocks = PP.oned_partition(0, 1, torch.zeros(n, 1), adj, True)
     blk = blocks[0]
-    old = ops.configure_core(enabled=True, step=64, max_side=1024, min_share=0.0, density=0.1, min_width=128)
+    old = ops.configure_core(enabled=True, step=64, max_side=1024, min_share=0.0, density=0.1, min_width=128, rounds=3)
     try:
         A = ops.CsrBlock.from_coo(blk.rows, blk.cols, blk.vals, n, n)
     finally:
         ops.configure_core(**old)
     assert A.core is not None, "this graph has a dense core at a 10 % density bar"
-    dense, core_rows, core_cols = A.core
-    assert int((dense != 0).sum()) + A.rest.nnz == A.nnz
-    assert len(set(core_rows.tolist())) == dense.size(0) and len(set(core_cols.tolist())) == dense.size(1)
+    src, in_cores, rounds = A, 0, 0
+    while src.core is not None:                   # one rectangle per round, each cut out of the previous rest
+        dense, core_rows, core_cols = src.core
+        assert int((dense != 0).sum()) + src.rest.nnz == src.nnz
+        assert len(set(core_rows.tolist())) == dense.size(0) and len(set(core_cols.tolist())) == dense.size(1)
+        in_cores += int((dense != 0).sum())
+        src, rounds = src.rest, rounds + 1
+    assert in_cores + src.nnz == A.nnz and 1 <= rounds <= 3
     g = torch.Generator().manual_seed(f)
     B, C0 = torch.randn(n, f, generator=g), torch.randn(n, f, generator=g)
     want = beta * C0.double() + torch.sparse.mm(_dense64(blk), B.double())
