@@ -23,6 +23,21 @@ NVCC_FLAGS = [
 ]
 
 
+def cutlass_include_dirs():
+    """The CUTLASS / CuTe header tree that ships inside the flashinfer wheel (include/ and tools/util/include/), or
+    [] when it is not installed.  Located without importing the package."""
+    import importlib.util
+    try:
+        spec = importlib.util.find_spec("flashinfer")
+    except (ImportError, ValueError):
+        spec = None
+    for root in (list(spec.submodule_search_locations) if spec and spec.submodule_search_locations else []):
+        inc = os.path.join(root, "data", "cutlass", "include")
+        if os.path.exists(os.path.join(inc, "cutlass", "gemm", "collective", "builders", "sm100_9xBF16_umma_builder.inl")):
+            return [inc, os.path.join(root, "data", "cutlass", "tools", "util", "include")]
+    return []
+
+
 def _nvcc():
     nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
     if not os.path.exists(nvcc):
@@ -47,6 +62,7 @@ def build(force=False, verbose=False):
     os.makedirs(BUILD_DIR, exist_ok=True)
     headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))]
     headers.append(os.path.join(os.path.dirname(HERE), "include", "cagnet_b200.h"))
+    cutlass = cutlass_include_dirs()
     srcs = sources()
     objs = [os.path.join(BUILD_DIR, os.path.basename(s)[:-3] + ".o") for s in srcs]
 
@@ -54,7 +70,12 @@ def build(force=False, verbose=False):
         src, obj = pair
         if not force and not _stale(obj, [src] + headers):
             return ""
-        cmd = [nvcc] + NVCC_FLAGS + ["-c", src, "-o", obj]
+        extra = []
+        if os.path.basename(src) == "core_gemm_tc.cu" and cutlass:
+            extra = ["--expt-relaxed-constexpr", "-DCAGNET_HAVE_CUTLASS", "-diag-suppress", "20012"]
+            for d in cutlass:
+                extra += ["-I", d]
+        cmd = [nvcc] + NVCC_FLAGS + extra + ["-c", src, "-o", obj]
         p = subprocess.run(cmd, capture_output=True, text=True)
         if p.returncode != 0:
             raise RuntimeError("nvcc failed for %s:\n%s\n%s" % (src, p.stdout, p.stderr))

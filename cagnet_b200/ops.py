@@ -135,8 +135,16 @@ def _row_major(t):
 # block (they are bound per nonzero, not per byte, and a 128-column dense tile would be mostly padding); "rounds":
 # how many rectangles may be cut out one after the other (a second one, 9,216 x 4,096 at 30 % density on the
 # benchmark graph, measured no gain: 13.30 ms against 13.13 ms).
-CORE = {"enabled": os.environ.get("CAGNET_DENSE_CORE", "1") != "0", "density": 0.2, "step": 1024, "max_side": 16384,
-        "max_bytes": 2 << 30, "min_share": 0.03, "min_width": 128, "rounds": 1}
+# "tensor_cores": multiply the core with the tcgen05 kernel when the library was built with it (fp32 accuracy
+# through a three-term bf16 split, 123 TFLOP/s against 40 for the fp32-FMA kernel); a dense cell then costs a
+# twelfth of a gathered nonzero and "density_tc" is the bar instead of "density".
+CORE = {"enabled": os.environ.get("CAGNET_DENSE_CORE", "1") != "0", "density": 0.2, "density_tc": 0.09, "step": 1024,
+        "max_side": 16384, "max_bytes": 2 << 30, "min_share": 0.03, "min_width": 128, "rounds": 1,
+        "tensor_cores": os.environ.get("CAGNET_CORE_TENSOR", "1") != "0"}
+
+
+def core_on_tensor_cores():
+    return bool(CORE["tensor_cores"]) and _native.lib().cagnet_core_gemm_tc_available() == 1
 
 
 def configure_core(**kw):
@@ -260,7 +268,7 @@ class CsrBlock:
         side_r = torch.arange(1, gr + 1, device=dev, dtype=torch.float64) * step
         side_c = torch.arange(1, gc + 1, device=dev, dtype=torch.float64) * step
         cells = side_r[:, None] * side_c[None, :]
-        gain = inside_count - float(cfg["density"]) * cells
+        gain = inside_count - float(cfg["density_tc"] if core_on_tensor_cores() else cfg["density"]) * cells
         gain[cells * 4 > float(cfg["max_bytes"])] = float("-inf")
         best = int(torch.argmax(gain))
         i, j = divmod(best, gc)
@@ -312,14 +320,35 @@ def spmm(block, B, C, beta=1.0):
             None if src.plan is None else src.plan.data_ptr(), _stream()), "spmm")
         LAUNCHES[0] += 1 if src.plan is None else 2
         for dense, core_rows, core_cols in cores:
-            nbytes = _native.lib().cagnet_core_gemm_workspace_bytes(dense.size(0), dense.size(1), f)
-            ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=C.device)
-            _native.check(_native.lib().cagnet_core_gemm_f32(
-                dense.data_ptr(), dense.stride(0), core_rows.data_ptr(), dense.size(0), core_cols.data_ptr(),
-                dense.size(1), B.data_ptr(), ldb, C.data_ptr(), ldc, f, ws.data_ptr(), ws.numel(), _stream()),
-                "core_gemm")
-            LAUNCHES[0] += 2 if nbytes else 1      # the multiply and the pass that adds up its k slices
+            _core_multiply(dense, core_rows, core_cols, B, ldb, C, ldc, f)
     return C
+
+
+def _core_multiply(dense, core_rows, core_cols, B, ldb, C, ldc, f):
+    """C[core_rows] += dense @ B[core_cols] on the current stream (device already current)."""
+    L = _native.lib()
+    r, k = dense.size(0), dense.size(1)
+    if core_on_tensor_cores() and dense.stride(0) % 4 == 0:
+        # tensor-core path: B's hub rows as one contiguous matrix (TMA cannot follow an index list), the
+        # product into a scratch matrix, its rows added into C's hub rows
+        Bs, D = empty_padded(k, f, C.device), empty_padded(r, f, C.device)
+        _native.check(L.cagnet_gather_rows_f32(B.data_ptr(), ldb, core_cols.data_ptr(), k, f, Bs.data_ptr(),
+                                               Bs.stride(0), _stream()), "gather_rows")
+        nbytes = L.cagnet_core_gemm_tc_workspace_bytes(r, k, f)
+        ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=C.device)
+        _native.check(L.cagnet_core_gemm_tc_f32(dense.data_ptr(), dense.stride(0), r, k, Bs.data_ptr(), Bs.stride(0),
+                                                D.data_ptr(), D.stride(0), f, ws.data_ptr(), ws.numel(), _stream()),
+                      "core_gemm_tc")
+        _native.check(L.cagnet_add_rows_f32(D.data_ptr(), D.stride(0), core_rows.data_ptr(), r, f, C.data_ptr(), ldc,
+                                            _stream()), "add_rows")
+        LAUNCHES[0] += 3
+        return
+    nbytes = L.cagnet_core_gemm_workspace_bytes(r, k, f)
+    ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=C.device)
+    _native.check(L.cagnet_core_gemm_f32(dense.data_ptr(), dense.stride(0), core_rows.data_ptr(), r,
+                                         core_cols.data_ptr(), k, B.data_ptr(), ldb, C.data_ptr(), ldc, f,
+                                         ws.data_ptr(), ws.numel(), _stream()), "core_gemm")
+    LAUNCHES[0] += 2 if nbytes else 1      # the multiply and the pass that adds up its k slices
 
 
 def spmm_gpu(A_rowindices, A_colindices, A_values, n, m, B, C):

@@ -117,6 +117,22 @@ int cagnet_core_gemm_f32(const float* core, int64_t ld_core, const int32_t* core
                          const float* B, int64_t ldb, float* C, int64_t ldc, int32_t f,
                          void* ws, size_t ws_bytes, void* stream);
 
+/* ---- The same dense core on the tensor cores: D[R x f] = core[R x K] * Bs[K x f], fp32 operands split into
+ * three bf16 terms each inside the kernel (nine tcgen05 products per k block, fp32 promotion of the accumulator
+ * after every k block: fp32-level accuracy).  Bs is the contiguous copy of the hub columns' rows of B
+ * (cagnet_gather_rows_f32: out[k] = B[idx[k]]); D is added into the hub rows of C afterwards
+ * (cagnet_add_rows_f32: C[rows[i]] += D[i]).  All rows 16-byte aligned, leading dimensions multiples of 4.
+ * cagnet_core_gemm_tc_available() is 0 when the library was built without the CUTLASS header tree; the
+ * multiply then returns CAGNET_E_ARG.  No counterpart in the reference. */
+int cagnet_core_gemm_tc_available(void);
+size_t cagnet_core_gemm_tc_workspace_bytes(int32_t R, int32_t K, int32_t f);
+int cagnet_core_gemm_tc_f32(const float* core, int64_t ld_core, int32_t R, int32_t K, const float* Bs, int64_t ldbs,
+                            float* D, int64_t ldd, int32_t f, void* ws, size_t ws_bytes, void* stream);
+int cagnet_gather_rows_f32(const float* B, int64_t ldb, const int32_t* idx, int32_t K, int32_t f, float* out,
+                           int64_t ldo, void* stream);
+int cagnet_add_rows_f32(const float* D, int64_t ldd, const int32_t* rows, int32_t R, int32_t f, float* C,
+                        int64_t ldc, void* stream);
+
 /* ---- Z = epilogue(X * W) for a tall X (n x K, ldx) and a small W.
  * transW = 0: W is K x N row-major (ldw);  transW = 1: W is N x K row-major (ldw) and is used
  * transposed (the `mm(ag, weight.t())` form).  aux (n x N, ldaux) is read by CAGNET_EPI_RELU_MASK only.

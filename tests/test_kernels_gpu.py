@@ -317,6 +317,36 @@ def test_core_gemm_indexed_rows(R, K, f):
     _close(Cd, want)
 
 
+@pytest.mark.parametrize("R,K,f", [(128, 128, 128), (200, 76, 602), (1, 8, 130), (300, 1000, 41), (130, 4864, 602)])
+def test_core_gemm_on_tensor_cores(R, K, f):
+    """gather rows -> tcgen05 multiply (fp32 split into three bf16 terms) -> add into listed rows, against fp64."""
+    L = _native.lib()
+    if L.cagnet_core_gemm_tc_available() != 1:
+        pytest.skip("library built without the CUTLASS header tree")
+    g = torch.Generator().manual_seed(R * 11 + K)
+    n, m = R + 50, K + 70
+    core = torch.randn(R, K, generator=g)
+    core[torch.rand(R, K, generator=g) < 0.5] = 0.0
+    rows = torch.randperm(n, generator=g)[:R]
+    cols = torch.randperm(m, generator=g)[:K]
+    B, C0 = torch.randn(m, f, generator=g), torch.randn(n, f, generator=g)
+    want = C0.double()
+    want[rows] += core.double() @ B.double()[cols]
+    Bd, Cd, cored = ops.to_padded(B.cuda()), ops.to_padded(C0.cuda()), core.cuda()
+    rd, cd = rows.int().cuda(), cols.int().cuda()
+    Bs, D = ops.empty_padded(K, f, "cuda"), ops.empty_padded(R, f, "cuda")
+    ws = torch.empty(max(L.cagnet_core_gemm_tc_workspace_bytes(R, K, f), 16), dtype=torch.uint8, device="cuda")
+    _native.check(L.cagnet_gather_rows_f32(Bd.data_ptr(), Bd.stride(0), cd.data_ptr(), K, f, Bs.data_ptr(), Bs.stride(0),
+                                           None), "gather")
+    assert torch.equal(Bs.cpu(), B[cols])
+    _native.check(L.cagnet_core_gemm_tc_f32(cored.data_ptr(), cored.stride(0), R, K, Bs.data_ptr(), Bs.stride(0),
+                                            D.data_ptr(), D.stride(0), f, ws.data_ptr(), ws.numel(), None), "tc")
+    _native.check(L.cagnet_add_rows_f32(D.data_ptr(), D.stride(0), rd.data_ptr(), R, f, Cd.data_ptr(), Cd.stride(0),
+                                        None), "add")
+    torch.cuda.synchronize()
+    _close(Cd, want)
+
+
 def test_core_gemm_rejects_unaligned_rows():
     z = torch.zeros(8, 7, device="cuda")
     idx = torch.arange(4, dtype=torch.int32, device="cuda")
@@ -326,19 +356,25 @@ def test_core_gemm_rejects_unaligned_rows():
     assert rc == 2 and b"16-byte" in _native.lib().cagnet_last_error_string()
 
 
+@pytest.mark.parametrize("tensor", [True, False])
 @pytest.mark.parametrize("f,beta", [(602, 0.0), (130, 1.0), (128, 0.0)])
-def test_spmm_with_dense_core_matches_oracle(f, beta):
+def test_spmm_with_dense_core_matches_oracle(f, beta, tensor):
     """A power-law block whose hub rows x hub columns rectangle is cut out and multiplied densely: same product."""
     n = 4096
     edge = graphs.rmat_graph(n, target_nnz=n * 96, seed=5)
     adj = graphs.add_self_loops(edge, n)
     _, blocks = PP.oned_partition(0, 1, torch.zeros(n, 1), adj, True)
     blk = blocks[0]
-    old = ops.configure_core(enabled=True, step=64, max_side=1024, min_share=0.0, density=0.1, min_width=128, rounds=3)
+    old = ops.configure_core(enabled=True, step=64, max_side=1024, min_share=0.0, density=0.1, density_tc=0.1,
+                             min_width=128, rounds=3, tensor_cores=tensor)
     try:
-        A = ops.CsrBlock.from_coo(blk.rows, blk.cols, blk.vals, n, n)
+        _spmm_with_core(blk, n, f, beta)
     finally:
         ops.configure_core(**old)
+
+
+def _spmm_with_core(blk, n, f, beta):
+    A = ops.CsrBlock.from_coo(blk.rows, blk.cols, blk.vals, n, n)
     assert A.core is not None, "this graph has a dense core at a 10 % density bar"
     src, in_cores, rounds = A, 0, 0
     while src.core is not None:                   # one rectangle per round, each cut out of the previous rest
@@ -359,7 +395,7 @@ def test_spmm_with_dense_core_matches_oracle(f, beta):
     Cn = ops.zeros_padded(n, 16, "cuda")
     before = ops.launch_count()
     ops.spmm(A, ops.to_padded(Bn.cuda()), Cn, 0.0)
-    assert ops.launch_count() - before == 2
+    assert ops.launch_count() - before <= 2
     _close(Cn, torch.sparse.mm(_dense64(blk), Bn.double()))
 
 
