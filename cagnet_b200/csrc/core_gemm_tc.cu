@@ -7,7 +7,7 @@
 // every k block, so that the result carries fp32 accuracy (not TF32's 10 bits) while the contraction itself runs
 // on the tensor pipe.  Of the nine cross products the three of order 2^-24 and below are left out (the builder's
 // default computes all nine; measured 2.66 ms against 2.74 ms at 16384^2 x 608, the same 1.3e-6 error against
-// fp64).  One CTA per 128 x 128 output tile, no cluster (and so no multicast loads), 1-SM MMA.
+// fp64).  One CTA per 128 x 128 output tile, cluster shape 1 x 1 x 1 (every CTA loads its own tiles), 1-SM MMA.
 // Measured: 123 TFLOP/s fp32-equivalent at 16384 x 16384 x 608, against 40 for the fp32-FMA kernel of
 // core_gemm.cu and 47-57 for the library SGEMM.
 //
