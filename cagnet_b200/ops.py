@@ -9,7 +9,7 @@ import os
 
 import torch
 
-from . import _native
+from . import _native, core_select
 
 EPI_NONE, EPI_RELU, EPI_LOG_SOFTMAX, EPI_RELU_MASK, EPI_ACCUMULATE = 0, 1, 2, 3, 4
 _INT32_MAX = 2 ** 31 - 1
@@ -157,15 +157,6 @@ def configure_core(**kw):
     return old
 
 
-def _top_by_degree(deg, limit):
-    """The `limit` highest-degree indices (ties by index, so the choice is reproducible) and, for every index, its
-    position in that list (`limit` for the ones left out)."""
-    order = torch.argsort(deg, descending=True, stable=True)[:limit]
-    rank = torch.full((deg.numel(),), limit, dtype=torch.int64, device=deg.device)
-    rank[order] = torch.arange(order.numel(), device=deg.device)
-    return order, rank
-
-
 # ------------------------------------------------------------------------------------------ sparse
 def coo2csr(rows, n):
     """rowptr[i] = #{e : rows[e] < i} for sorted int32 row indices on the device (int32, n + 1 entries)."""
@@ -247,47 +238,20 @@ class CsrBlock:
         to CORE["rounds"] rectangles.  Runs once per block, with torch index kernels on the block's device; the
         choice depends only on the block (ties broken by index)."""
         cfg = CORE
-        step = int(cfg["step"])
-        if not cfg["enabled"] or self.nnz == 0 or step <= 0:
+        if not cfg["enabled"]:
             return
-        gr, gc = min(cfg["max_side"], self.n) // step, min(cfg["max_side"], self.m) // step
-        if gr == 0 or gc == 0:
+        bar = cfg["density_tc"] if core_on_tensor_cores() else cfg["density"]
+        choice = core_select.choose_core(self.rowptr, self.col, self.n, self.m, bar, cfg["step"], cfg["max_side"],
+                                         cfg["max_bytes"], cfg["min_share"])
+        if choice is None:
             return
-        dev = self.val.device
-        rowptr = self.rowptr.long()
-        deg_r = rowptr[1:] - rowptr[:-1]
-        col = self.col.long()
-        deg_c = torch.bincount(col, minlength=self.m)
-        order_r, rank_r = _top_by_degree(deg_r, gr * step)
-        order_c, rank_c = _top_by_degree(deg_c, gc * step)
-        row_of = torch.repeat_interleave(torch.arange(self.n, device=dev), deg_r)
-        er, ec = rank_r[row_of], rank_c[col]
-        inside = (er < gr * step) & (ec < gc * step)
-        hist = torch.bincount((er[inside] // step) * gc + ec[inside] // step, minlength=gr * gc).view(gr, gc)
-        inside_count = hist.cumsum(0).cumsum(1).double()
-        side_r = torch.arange(1, gr + 1, device=dev, dtype=torch.float64) * step
-        side_c = torch.arange(1, gc + 1, device=dev, dtype=torch.float64) * step
-        cells = side_r[:, None] * side_c[None, :]
-        gain = inside_count - float(cfg["density_tc"] if core_on_tensor_cores() else cfg["density"]) * cells
-        gain[cells * 4 > float(cfg["max_bytes"])] = float("-inf")
-        best = int(torch.argmax(gain))
-        i, j = divmod(best, gc)
-        if not float(gain[i, j]) >= float(cfg["min_share"]) * self.nnz:
-            return
-        r, c = (i + 1) * step, (j + 1) * step
-        in_core = (er < r) & (ec < c)
-        dense = torch.zeros(r, c, dtype=torch.float32, device=dev)
-        dense.index_put_((er[in_core], ec[in_core]), self.val[in_core], accumulate=True)
-        keep = ~in_core
-        kept = deg_r - torch.bincount(row_of[in_core], minlength=self.n)
-        rest_rowptr = torch.zeros(self.n + 1, dtype=torch.int32, device=dev)
-        rest_rowptr[1:] = torch.cumsum(kept, 0).int()
-        rest = CsrBlock(rest_rowptr, self.col[keep].contiguous(), self.val[keep].contiguous(), self.n, self.m)
+        dense, rest_rowptr, rest_col, rest_val = core_select.split_core(self.col, self.val, self.n, choice)
+        rest = CsrBlock(rest_rowptr, rest_col, rest_val, self.n, self.m)
         rest.build_plan(core=False)
         if depth + 1 < int(cfg["rounds"]):
             rest.extract_core(depth + 1)
         self.rest = rest
-        self.core = (dense, order_r[:r].int().contiguous(), order_c[:c].int().contiguous())
+        self.core = (dense, choice.rows.int().contiguous(), choice.cols.int().contiguous())
 
     def long_rows(self):
         """Number of rows the plan routes to the block-per-row kernel (synchronises)."""
