@@ -292,7 +292,7 @@ def run_ours(args):
                        "vertices": info["n"], "l2": "inputs larger than L2 (CSR 0.92 GB + features 0.56 GB per epoch)"},
             "spmm_gbs": all_alg / all_ms / 1e6 if all_ms > 0 else None,
             "spmm_ms_per_epoch": all_ms / args.steps,
-            "roofline": {"bound": "hbm", "kernel": "spmm f=602 (hub-row and warp-per-row launches on the sparse part; gather, tcgen05 multiply and row-add launches on the dense core)",
+            "roofline": {"bound": "hbm", "kernel": "spmm f=602 (hub-row and warp-per-row launches on the sparse part; gather+split, tcgen05 3xTF32 multiplies in k chunks and row-add launches on the dense core)",
                          "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_source": peak_kind, "launch_ms": wide_ms / max(len(wide), 1),
                          "traffic": spmm_traffic_bytes()},

@@ -28,9 +28,10 @@ PROTOTYPES = {
     "cagnet_core_gemm_f32": (_i32, [_vp, _i64, _vp, _i32, _vp, _i32, _vp, _i64, _vp, _i64, _i32, _vp, _sz, _vp]),
     "cagnet_core_gemm_tc_available": (_i32, []),
     "cagnet_core_gemm_tc_workspace_bytes": (_sz, [_i32, _i32, _i32]),
-    "cagnet_core_gemm_tc_f32": (_i32, [_vp, _i64, _i32, _i32, _vp, _i64, _vp, _i64, _i32, _vp, _sz, _vp]),
-    "cagnet_gather_rows_f32": (_i32, [_vp, _i64, _vp, _i32, _i32, _vp, _i64, _vp]),
-    "cagnet_add_rows_f32": (_i32, [_vp, _i64, _vp, _i32, _i32, _vp, _i64, _vp]),
+    "cagnet_split_tf32_f32": (_i32, [_vp, _i64, _vp, _vp, _vp]),
+    "cagnet_gather_split_rows_f32": (_i32, [_vp, _i64, _vp, _i32, _i32, _vp, _i64, _vp]),
+    "cagnet_core_gemm_tc_f32": (_i32, [_vp, _vp, _i64, _i32, _i32, _vp, _i64, _vp, _i32, _vp, _sz, _vp]),
+    "cagnet_add_rows3_f32": (_i32, [_vp, _i64, _vp, _i32, _i32, _vp, _i64, _vp]),
     "cagnet_gemm_nn_f32": (_i32, [_vp, _i64, _vp, _i64, _i32, _vp, _i64, _i64, _i32, _i32, _i32, _vp, _i64, _vp]),
     "cagnet_gemm_tn_workspace_bytes": (_sz, [_i64, _i32, _i32]),
     "cagnet_gemm_tn_f32": (_i32, [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _i32, _i32, _f32, _vp, _sz, _vp]),

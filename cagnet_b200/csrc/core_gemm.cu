@@ -180,19 +180,6 @@ core_reduce_kernel(const float* __restrict__ ws, int64_t ldw, int parts, const i
   if (n + 3 < f) c[3] += sum.w;
 }
 
-// out[k, 0:f) = B[idx[k], 0:f): the hub columns' rows of B as one contiguous matrix (the tensor-core multiply
-// reads its operands through TMA descriptors, which cannot follow an index list).  One thread per float4.
-__global__ void __launch_bounds__(256)
-gather_rows_kernel(const float* __restrict__ B, int64_t ldb, const int* __restrict__ idx, int K, int f,
-                   float* __restrict__ out, int64_t ldo) {
-  const int vecs = (f + 3) / 4;
-  const int64_t t = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (t >= static_cast<int64_t>(K) * vecs) return;
-  const int k = static_cast<int>(t / vecs), n = static_cast<int>(t % vecs) * 4;
-  const float4 v = __ldg(reinterpret_cast<const float4*>(B + static_cast<int64_t>(__ldg(idx + k)) * ldb + n));
-  *reinterpret_cast<float4*>(out + static_cast<int64_t>(k) * ldo + n) = v;
-}
-
 // How many k slices: enough blocks for about six full waves of 2 blocks per SM, so that the last wave's idle SMs
 // cost little, but never slices shorter than 16 k steps.
 static int core_parts(int R, int K, int f) {
@@ -244,31 +231,4 @@ extern "C" int cagnet_core_gemm_f32(const float* core, int64_t ld_core, const in
                                                                                    parts, core_rows, R, C, ldc, f);
   }
   return check_launch("cagnet_core_gemm_f32");
-}
-
-extern "C" int cagnet_gather_rows_f32(const float* B, int64_t ldb, const int32_t* idx, int32_t K, int32_t f, float* out,
-                                      int64_t ldo, void* stream) {
-  if (K < 0 || f < 0) return fail(CAGNET_E_ARG, "cagnet_gather_rows_f32: negative size");
-  if (K == 0 || f == 0) return CAGNET_OK;
-  if (!B || !idx || !out) return fail(CAGNET_E_ARG, "cagnet_gather_rows_f32: null pointer");
-  const int64_t f4 = (static_cast<int64_t>(f) + 3) / 4 * 4;
-  if (ldb < f4 || ldo < f4 || ldb % 4 || ldo % 4 || !aligned(B, 16) || !aligned(out, 16))
-    return fail(CAGNET_E_ALIGN, "cagnet_gather_rows_f32: rows must be padded to a multiple of 4 floats and 16-byte aligned");
-  const int64_t threads = static_cast<int64_t>(K) * (f4 / 4);
-  gather_rows_kernel<<<static_cast<unsigned>((threads + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      B, ldb, idx, K, f, out, ldo);
-  return check_launch("cagnet_gather_rows_f32");
-}
-
-extern "C" int cagnet_add_rows_f32(const float* D, int64_t ldd, const int32_t* rows, int32_t R, int32_t f, float* C,
-                                   int64_t ldc, void* stream) {
-  if (R < 0 || f < 0) return fail(CAGNET_E_ARG, "cagnet_add_rows_f32: negative size");
-  if (R == 0 || f == 0) return CAGNET_OK;
-  if (!D || !rows || !C) return fail(CAGNET_E_ARG, "cagnet_add_rows_f32: null pointer");
-  if (ldd < f || ldc < f || ldd % 4 || !aligned(D, 16))
-    return fail(CAGNET_E_ALIGN, "cagnet_add_rows_f32: D rows must be padded to a multiple of 4 floats and 16-byte aligned");
-  const int64_t threads = static_cast<int64_t>(R) * (ldd / 4);
-  core_reduce_kernel<<<static_cast<unsigned>((threads + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      D, ldd, 1, rows, R, C, ldc, f);
-  return check_launch("cagnet_add_rows_f32");
 }

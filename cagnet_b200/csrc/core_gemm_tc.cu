@@ -1,21 +1,91 @@
 // Dense core of a power-law adjacency block on the 5th-generation tensor cores (tcgen05 / TMEM) of sm_100a.
 //
-// D[R x f] = core[R x K] * Bs[K x f], all fp32 in memory.  The multiply runs as CUTLASS's sm100 "fast FP32"
-// mainloop: TMA brings fp32 tiles of both operands into shared memory, transform warps split every value into
-// three bf16 terms (x = x1 + 2^-8 x2 + 2^-16 x3; the terms of A go to TMEM, those of B back to shared memory),
-// tcgen05.mma accumulates the cross products into TMEM, and the accumulator is promoted to fp32 registers after
-// every k block, so that the result carries fp32 accuracy (not TF32's 10 bits) while the contraction itself runs
-// on the tensor pipe.  Of the nine cross products the three of order 2^-24 and below are left out (the builder's
-// default computes all nine; measured 2.66 ms against 2.74 ms at 16384^2 x 608, the same 1.3e-6 error against
-// fp64).  One CTA per 128 x 128 output tile, cluster shape 1 x 1 x 1 (every CTA loads its own tiles), 1-SM MMA.
-// Measured: 123 TFLOP/s fp32-equivalent at 16384 x 16384 x 608, against 40 for the fp32-FMA kernel of
-// core_gemm.cu and 47-57 for the library SGEMM.
+// D = core[R x K] * Bs[K x f] with fp32 accuracy from TF32 tensor-core products ("3xTF32"): every operand is
+// split once into hi = its value rounded to TF32's 11 significant bits and lo = the remainder (exact in fp32),
+// and
+//     core * Bs  ~  core_hi * Bs_hi  +  (core_hi * Bs_lo + core_lo * Bs_hi)          (lo * lo ~ 2^-22 is dropped).
+// The core is static, so its split is made once when the block is planned; the hub columns' rows of B are
+// gathered and split in one pass per multiply (gather_split_rows_kernel writes [Bs_hi | Bs_lo] side by side, so
+// core_hi needs a single GEMM against both).  The GEMMs are CUTLASS's sm100 TMA + tcgen05.mma (kind::tf32)
+// warp-specialised mainloop, instantiated here: 128 x 128 x 32 tiles, accumulators in TMEM, cluster shape
+// 1 x 1 x 1 (every CTA loads its own tiles), 1-SM MMA.
 //
-// This file only instantiates the CUTLASS / CuTe templates (header tree found at build time); the gather of B's
-// rows before it and the addition of D into C's rows after it are kernels of this library (core_gemm.cu).
-// Without the header tree the file compiles to a stub that reports CAGNET_E_ARG, and the host layer keeps using
-// the fp32-FMA kernel.
+// Accuracy: a tensor-core accumulator is not a round-to-nearest fp32 sum, and its error grows with the length of
+// the contraction (measured 2.8e-5 of the largest magnitude at k = 13,312 in one piece).  The k range is
+// therefore cut into chunks of kChunk; each chunk's GEMM adds into D in its epilogue (beta = 1), which is a
+// proper fp32 addition.
+//
+// This file instantiates CUTLASS / CuTe templates (header tree found at build time) and adds the split kernels
+// around them.  Without the header tree it compiles to a stub that reports CAGNET_E_ARG, and the host layer
+// keeps using the fp32-FMA kernel of core_gemm.cu.
 #include "common.cuh"
+
+namespace cagnet {
+
+__device__ __forceinline__ float tf32_round(float x) {
+  // nearest value with 10 explicit mantissa bits (ties away from zero; the remainder stays exact either way)
+  return __int_as_float((__float_as_int(x) + 0x1000) & ~0x1fff);
+}
+
+__global__ void __launch_bounds__(256)
+split_tf32_kernel(const float* __restrict__ x, int64_t count, float* __restrict__ hi, float* __restrict__ lo) {
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < count;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const float v = x[i];
+    const float h = tf32_round(v);
+    hi[i] = h;
+    lo[i] = v - h;
+  }
+}
+
+// out[k, n] = hi(B[idx[k], n]), out[k, half + n] = lo(B[idx[k], n]) for n < f; columns [f, half) of both halves
+// are written as zeros.  One thread per float4 of a gathered row.
+__global__ void __launch_bounds__(256)
+gather_split_rows_kernel(const float* __restrict__ B, int64_t ldb, const int* __restrict__ idx, int K, int f,
+                         float* __restrict__ out, int64_t half) {
+  const int vecs = static_cast<int>(half / 4);
+  const int64_t t = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (t >= static_cast<int64_t>(K) * vecs) return;
+  const int k = static_cast<int>(t / vecs), n = static_cast<int>(t % vecs) * 4;
+  float v[4] = {0.f, 0.f, 0.f, 0.f};
+  if (n < f) {
+    const float4 q = __ldg(reinterpret_cast<const float4*>(B + static_cast<int64_t>(__ldg(idx + k)) * ldb + n));
+    v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w;
+  }
+  float h[4], l[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    if (n + j >= f) v[j] = 0.f;
+    h[j] = tf32_round(v[j]);
+    l[j] = v[j] - h[j];
+  }
+  float* row = out + static_cast<int64_t>(k) * 2 * half;
+  *reinterpret_cast<float4*>(row + n) = make_float4(h[0], h[1], h[2], h[3]);
+  *reinterpret_cast<float4*>(row + half + n) = make_float4(l[0], l[1], l[2], l[3]);
+}
+
+// C[rows[m], n] += D[m, n] + (D[m, half + n] + D[m, 2 half + n]): the hi*hi product plus the two cross products
+// (small terms added to each other first).  One thread per float4.
+__global__ void __launch_bounds__(256)
+add_rows3_kernel(const float* __restrict__ D, int64_t half, const int* __restrict__ rows, int R,
+                 float* __restrict__ C, int64_t ldc, int f) {
+  const int vecs = static_cast<int>(half / 4);
+  const int64_t t = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (t >= static_cast<int64_t>(R) * vecs) return;
+  const int m = static_cast<int>(t / vecs), n = static_cast<int>(t % vecs) * 4;
+  if (n >= f) return;
+  const float* d = D + static_cast<int64_t>(m) * 3 * half + n;
+  const float4 a = __ldg(reinterpret_cast<const float4*>(d));
+  const float4 b = __ldg(reinterpret_cast<const float4*>(d + half));
+  const float4 c = __ldg(reinterpret_cast<const float4*>(d + 2 * half));
+  float* out = C + static_cast<int64_t>(__ldg(rows + m)) * ldc + n;
+  if (n + 0 < f) out[0] += a.x + (b.x + c.x);
+  if (n + 1 < f) out[1] += a.y + (b.y + c.y);
+  if (n + 2 < f) out[2] += a.z + (b.z + c.z);
+  if (n + 3 < f) out[3] += a.w + (b.w + c.w);
+}
+
+}  // namespace cagnet
 
 #ifdef CAGNET_HAVE_CUTLASS
 
@@ -34,66 +104,66 @@ namespace tc {
 
 using namespace cute;
 
-using ElementA = float;                         // core, row-major R x K  (K contiguous)
-using ElementB = float;                         // Bs, row-major K x f    (f contiguous: "row-major B")
-using ElementC = float;
-using ElementAcc = float;
-using LayoutA = cutlass::layout::RowMajor;
-using LayoutB = cutlass::layout::RowMajor;
+using LayoutA = cutlass::layout::RowMajor;      // core: R x K, k contiguous
+using LayoutB = cutlass::layout::RowMajor;      // [Bs_hi | Bs_lo]: K x N, n contiguous
 using LayoutC = cutlass::layout::RowMajor;
 constexpr int kAlign = 4;                       // 16-byte rows for TMA
 
-using MmaTile = Shape<_128, _128, _32>;
+using MmaTile = Shape<_128, _128, _32>;         // 128 x 256 tiles measured slower (1.24 against 1.02 ms at 13312^2)
 using Cluster = Shape<_1, _1, _1>;
 
 using Epilogue = typename cutlass::epilogue::collective::CollectiveBuilder<
     cutlass::arch::Sm100, cutlass::arch::OpClassTensorOp, MmaTile, Cluster,
-    cutlass::epilogue::collective::EpilogueTileAuto, ElementAcc, ElementAcc, ElementC, LayoutC, kAlign, ElementC,
-    LayoutC, kAlign, cutlass::epilogue::FastF32NoSmemWarpSpecialized1Sm>::CollectiveOp;
+    cutlass::epilogue::collective::EpilogueTileAuto, float, float, float, LayoutC, kAlign, float, LayoutC, kAlign,
+    cutlass::epilogue::collective::EpilogueScheduleAuto>::CollectiveOp;
 
-using Built = typename cutlass::gemm::collective::CollectiveBuilder<
-    cutlass::arch::Sm100, cutlass::arch::OpClassTensorOp, ElementA, LayoutA, kAlign, ElementB, LayoutB, kAlign,
-    ElementAcc, MmaTile, Cluster,
+// float operands on the tensor-op class = tcgen05.mma kind::tf32
+using Mainloop = typename cutlass::gemm::collective::CollectiveBuilder<
+    cutlass::arch::Sm100, cutlass::arch::OpClassTensorOp, float, LayoutA, kAlign, float, LayoutB, kAlign, float,
+    MmaTile, Cluster,
     cutlass::gemm::collective::StageCountAutoCarveout<static_cast<int>(sizeof(typename Epilogue::SharedStorage))>,
-    cutlass::gemm::KernelTmaWarpSpecialized1SmFastFP32Sm100>::CollectiveOp;
-
-// the builder's mainloop with one change: 3 bands (6 cross products) instead of 5 (9)
-constexpr int kBands = 3;
-using BuiltPolicy = typename Built::DispatchPolicy;
-using Policy = cutlass::gemm::MainloopSm100TmaUmmaWarpSpecializedFastF32<
-    BuiltPolicy::Load2TransformPipelineStageCount, BuiltPolicy::Transform2MmaPipelineStageCount,
-    BuiltPolicy::Schedule::SchedulerPipelineStageCount, BuiltPolicy::Schedule::AccumulatorPipelineStageCount, kBands,
-    BuiltPolicy::ScalingFactor, BuiltPolicy::AccPromotionInterval, typename BuiltPolicy::ClusterShape,
-    typename BuiltPolicy::AccumulatorCopyAtom, typename BuiltPolicy::ArchTag>;
-using Mainloop = cutlass::gemm::collective::CollectiveMma<
-    Policy, typename Built::TileShape, float, typename Built::StrideA, float, typename Built::StrideB,
-    typename Built::TiledMma, typename Built::GmemTiledCopyA, typename Built::SmemLayoutAtomsA,
-    typename Built::CopyAtomsA, typename Built::TransformA, typename Built::GmemTiledCopyB,
-    typename Built::SmemLayoutAtomsB, typename Built::CopyAtomsB, typename Built::TransformB>;
+    cutlass::gemm::collective::KernelScheduleAuto>::CollectiveOp;
 
 using Kernel = cutlass::gemm::kernel::GemmUniversal<Shape<int, int, int, int>, Mainloop, Epilogue>;
 using Gemm = cutlass::gemm::device::GemmUniversalAdapter<Kernel>;
 
-static typename Gemm::Arguments make_args(const float* core, int64_t ld_core, int R, int K, const float* Bs, int64_t ldbs,
-                                          float* D, int64_t ldd, int f) {
+constexpr int kChunk = 2048;                    // k length of one tensor-core accumulation
+
+static typename Gemm::Arguments make_args(const float* A, int64_t lda, const float* B, int64_t ldb, float* D,
+                                          int64_t ldd, int M, int N, int K, float beta) {
   using StrideA = typename Kernel::StrideA;
   using StrideB = typename Kernel::StrideB;
   using StrideC = typename Kernel::StrideC;
   using StrideD = typename Kernel::StrideD;
-  StrideA sa = cutlass::make_cute_packed_stride(StrideA{}, cute::make_shape(R, K, 1));
-  StrideB sb = cutlass::make_cute_packed_stride(StrideB{}, cute::make_shape(f, K, 1));
-  StrideC sc = cutlass::make_cute_packed_stride(StrideC{}, cute::make_shape(R, f, 1));
-  StrideD sd = cutlass::make_cute_packed_stride(StrideD{}, cute::make_shape(R, f, 1));
+  StrideA sa = cutlass::make_cute_packed_stride(StrideA{}, cute::make_shape(M, K, 1));
+  StrideB sb = cutlass::make_cute_packed_stride(StrideB{}, cute::make_shape(N, K, 1));
+  StrideC sc = cutlass::make_cute_packed_stride(StrideC{}, cute::make_shape(M, N, 1));
+  StrideD sd = cutlass::make_cute_packed_stride(StrideD{}, cute::make_shape(M, N, 1));
   // leading dimensions of the padded layouts (the packed helpers assume ld == extent)
-  cute::get<0>(sa) = ld_core;
-  cute::get<1>(sb) = ldbs;
+  cute::get<0>(sa) = lda;
+  cute::get<1>(sb) = ldb;
   cute::get<0>(sc) = ldd;
   cute::get<0>(sd) = ldd;
-  typename Gemm::Arguments args{cutlass::gemm::GemmUniversalMode::kGemm,
-                                {R, f, K, 1},
-                                {core, sa, Bs, sb},
-                                {{1.0f, 0.0f}, D, sc, D, sd}};
-  return args;
+  return typename Gemm::Arguments{cutlass::gemm::GemmUniversalMode::kGemm,
+                                  {M, N, K, 1},
+                                  {A, sa, B, sb},
+                                  {{1.0f, beta}, D, sc, D, sd}};
+}
+
+// D (ldd) = beta * D + A (lda) * B (ldb) on `stream`
+static int gemm(const float* A, int64_t lda, const float* B, int64_t ldb, float* D, int64_t ldd, int M, int N, int K,
+                float beta, void* ws, size_t ws_bytes, cudaStream_t stream) {
+  auto args = make_args(A, lda, B, ldb, D, ldd, M, N, K, beta);
+  if (Gemm::get_workspace_size(args) > ws_bytes)
+    return fail(CAGNET_E_WORKSPACE, "cagnet_core_gemm_tc_f32: workspace too small");
+  Gemm op;
+  if (op.can_implement(args) != cutlass::Status::kSuccess)
+    return fail(CAGNET_E_ARG, "cagnet_core_gemm_tc_f32: shape or alignment not supported by the tensor-core mainloop");
+  if (op.initialize(args, ws, stream) != cutlass::Status::kSuccess)
+    return fail(CAGNET_E_LAUNCH, "cagnet_core_gemm_tc_f32: initialisation of the tensor-core multiply failed");
+  if (op.run(stream) != cutlass::Status::kSuccess)
+    return fail(CAGNET_E_LAUNCH, "cagnet_core_gemm_tc_f32: launch of the tensor-core multiply failed");
+  return CAGNET_OK;
 }
 
 }  // namespace tc
@@ -105,36 +175,33 @@ extern "C" int cagnet_core_gemm_tc_available(void) { return 1; }
 
 extern "C" size_t cagnet_core_gemm_tc_workspace_bytes(int32_t R, int32_t K, int32_t f) {
   if (R <= 0 || K <= 0 || f <= 0) return 0;
-  const int f4 = (f + 3) / 4 * 4;
-  auto args = tc::make_args(nullptr, K, R, K, nullptr, f4, nullptr, f4, f4);
+  const int half = (f + 3) / 4 * 4;
+  auto args = tc::make_args(nullptr, K, nullptr, 2 * half, nullptr, 3 * half, R, 2 * half, K < tc::kChunk ? K : tc::kChunk, 0.f);
   return tc::Gemm::get_workspace_size(args) + 16;
 }
 
-extern "C" int cagnet_core_gemm_tc_f32(const float* core, int64_t ld_core, int32_t R, int32_t K, const float* Bs,
-                                       int64_t ldbs, float* D, int64_t ldd, int32_t f, void* ws, size_t ws_bytes,
+extern "C" int cagnet_core_gemm_tc_f32(const float* core_hi, const float* core_lo, int64_t ld_core, int32_t R, int32_t K,
+                                       const float* Bs, int64_t half, float* D, int32_t f, void* ws, size_t ws_bytes,
                                        void* stream) {
   if (R < 0 || K < 0 || f < 0) return fail(CAGNET_E_ARG, "cagnet_core_gemm_tc_f32: negative size");
   if (R == 0 || K == 0 || f == 0) return CAGNET_OK;
-  if (!core || !Bs || !D) return fail(CAGNET_E_ARG, "cagnet_core_gemm_tc_f32: null pointer");
-  if (ld_core < K || ldbs < f || ldd < f) return fail(CAGNET_E_ARG, "cagnet_core_gemm_tc_f32: leading dimension too small");
-  if (ld_core % 4 || ldbs % 4 || ldd % 4 || !aligned(core, 16) || !aligned(Bs, 16) || !aligned(D, 16))
-    return fail(CAGNET_E_ALIGN, "cagnet_core_gemm_tc_f32: rows of core, Bs and D must start on 16-byte boundaries");
-  // the mainloop wants whole 16-byte vectors along f: columns [f, f4) are pad columns of Bs and D (their values
-  // are unspecified on the way in and on the way out; no other column depends on them)
-  const int f4 = (f + 3) / 4 * 4;
-  if (ldbs < f4 || ldd < f4) return fail(CAGNET_E_ARG, "cagnet_core_gemm_tc_f32: rows must be padded to a multiple of 4 floats");
-  auto args = tc::make_args(core, ld_core, R, K, Bs, ldbs, D, ldd, f4);
-  const size_t need = tc::Gemm::get_workspace_size(args);
-  if (need && (!ws || ws_bytes < need))
-    return fail(CAGNET_E_WORKSPACE, "cagnet_core_gemm_tc_f32: workspace of %s%lld bytes is too small (need %lld)", "",
-                (long long)ws_bytes, (long long)need);
-  tc::Gemm gemm;
-  if (gemm.can_implement(args) != cutlass::Status::kSuccess)
-    return fail(CAGNET_E_ARG, "cagnet_core_gemm_tc_f32: shape or alignment not supported by the tensor-core mainloop");
-  if (gemm.initialize(args, ws, static_cast<cudaStream_t>(stream)) != cutlass::Status::kSuccess)
-    return fail(CAGNET_E_LAUNCH, "cagnet_core_gemm_tc_f32: initialisation of the tensor-core multiply failed");
-  if (gemm.run(static_cast<cudaStream_t>(stream)) != cutlass::Status::kSuccess)
-    return fail(CAGNET_E_LAUNCH, "cagnet_core_gemm_tc_f32: launch of the tensor-core multiply failed");
+  if (!core_hi || !core_lo || !Bs || !D) return fail(CAGNET_E_ARG, "cagnet_core_gemm_tc_f32: null pointer");
+  if (ld_core < K || half < f) return fail(CAGNET_E_ARG, "cagnet_core_gemm_tc_f32: leading dimension too small");
+  if (ld_core % 4 || half % 4 || !aligned(core_hi, 16) || !aligned(core_lo, 16) || !aligned(Bs, 16) || !aligned(D, 16))
+    return fail(CAGNET_E_ALIGN, "cagnet_core_gemm_tc_f32: rows of the core, Bs and D must start on 16-byte boundaries");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int n1 = static_cast<int>(2 * half), n2 = static_cast<int>(half);
+  for (int k0 = 0; k0 < K; k0 += tc::kChunk) {
+    const int kc = (K - k0 < tc::kChunk) ? K - k0 : tc::kChunk;
+    const float beta = k0 == 0 ? 0.f : 1.f;
+    const float* b = Bs + static_cast<int64_t>(k0) * 2 * half;
+    // D[:, 0:2 half) (+)= core_hi[:, k0:k0+kc) * [Bs_hi | Bs_lo][k0:k0+kc)
+    int rc = tc::gemm(core_hi + k0, ld_core, b, 2 * half, D, 3 * half, R, n1, kc, beta, ws, ws_bytes, s);
+    if (rc) return rc;
+    // D[:, 2 half:3 half) (+)= core_lo[:, k0:k0+kc) * Bs_hi[k0:k0+kc)
+    rc = tc::gemm(core_lo + k0, ld_core, b, 2 * half, D + 2 * half, 3 * half, R, n2, kc, beta, ws, ws_bytes, s);
+    if (rc) return rc;
+  }
   return check_launch("cagnet_core_gemm_tc_f32");
 }
 
@@ -144,9 +211,46 @@ using namespace cagnet;
 
 extern "C" int cagnet_core_gemm_tc_available(void) { return 0; }
 extern "C" size_t cagnet_core_gemm_tc_workspace_bytes(int32_t, int32_t, int32_t) { return 0; }
-extern "C" int cagnet_core_gemm_tc_f32(const float*, int64_t, int32_t, int32_t, const float*, int64_t, float*, int64_t,
-                                       int32_t, void*, size_t, void*) {
+extern "C" int cagnet_core_gemm_tc_f32(const float*, const float*, int64_t, int32_t, int32_t, const float*, int64_t,
+                                       float*, int32_t, void*, size_t, void*) {
   return fail(CAGNET_E_ARG, "cagnet_core_gemm_tc_f32: built without the CUTLASS header tree");
 }
 
 #endif
+
+extern "C" int cagnet_split_tf32_f32(const float* x, int64_t count, float* hi, float* lo, void* stream) {
+  if (count < 0) return fail(CAGNET_E_ARG, "cagnet_split_tf32_f32: negative size");
+  if (count == 0) return CAGNET_OK;
+  if (!x || !hi || !lo) return fail(CAGNET_E_ARG, "cagnet_split_tf32_f32: null pointer");
+  const int64_t blocks = (count + 255) / 256;
+  split_tf32_kernel<<<static_cast<unsigned>(blocks < 16 * kNumSMs ? blocks : 16 * kNumSMs), 256, 0,
+                      static_cast<cudaStream_t>(stream)>>>(x, count, hi, lo);
+  return check_launch("cagnet_split_tf32_f32");
+}
+
+extern "C" int cagnet_gather_split_rows_f32(const float* B, int64_t ldb, const int32_t* idx, int32_t K, int32_t f,
+                                            float* out, int64_t half, void* stream) {
+  if (K < 0 || f < 0) return fail(CAGNET_E_ARG, "cagnet_gather_split_rows_f32: negative size");
+  if (K == 0 || f == 0) return CAGNET_OK;
+  if (!B || !idx || !out) return fail(CAGNET_E_ARG, "cagnet_gather_split_rows_f32: null pointer");
+  const int64_t f4 = (static_cast<int64_t>(f) + 3) / 4 * 4;
+  if (ldb < f4 || half < f4 || ldb % 4 || half % 4 || !aligned(B, 16) || !aligned(out, 16))
+    return fail(CAGNET_E_ALIGN, "cagnet_gather_split_rows_f32: rows must be padded to a multiple of 4 floats and 16-byte aligned");
+  const int64_t threads = static_cast<int64_t>(K) * (half / 4);
+  gather_split_rows_kernel<<<static_cast<unsigned>((threads + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      B, ldb, idx, K, f, out, half);
+  return check_launch("cagnet_gather_split_rows_f32");
+}
+
+extern "C" int cagnet_add_rows3_f32(const float* D, int64_t half, const int32_t* rows, int32_t R, int32_t f, float* C,
+                                    int64_t ldc, void* stream) {
+  if (R < 0 || f < 0) return fail(CAGNET_E_ARG, "cagnet_add_rows3_f32: negative size");
+  if (R == 0 || f == 0) return CAGNET_OK;
+  if (!D || !rows || !C) return fail(CAGNET_E_ARG, "cagnet_add_rows3_f32: null pointer");
+  if (half < f || ldc < f || half % 4 || !aligned(D, 16))
+    return fail(CAGNET_E_ALIGN, "cagnet_add_rows3_f32: D rows must be padded to a multiple of 4 floats and 16-byte aligned");
+  const int64_t threads = static_cast<int64_t>(R) * (half / 4);
+  add_rows3_kernel<<<static_cast<unsigned>((threads + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      D, half, rows, R, C, ldc, f);
+  return check_launch("cagnet_add_rows3_f32");
+}

@@ -181,6 +181,7 @@ class CsrBlock:
         self.rowptr, self.col, self.val, self.n, self.m, self.plan = rowptr, col, val, int(n), int(m), plan
         self.nnz = int(val.numel())
         self.core = self.rest = None      # dense hub-by-hub rectangle and the CSR block of everything else
+        self.core_split = None            # the rectangle as TF32 hi + lo parts (tensor-core multiply)
 
     @staticmethod
     def from_coo(rows, cols, vals, n, m, validate=True, plan=True):
@@ -252,6 +253,14 @@ class CsrBlock:
             rest.extract_core(depth + 1)
         self.rest = rest
         self.core = (dense, choice.rows.int().contiguous(), choice.cols.int().contiguous())
+        self.core_split = None
+        if core_on_tensor_cores() and dense.stride(0) % 4 == 0:
+            hi, lo = torch.empty_like(dense), torch.empty_like(dense)
+            with _on(dense.device):
+                _native.check(_native.lib().cagnet_split_tf32_f32(dense.data_ptr(), dense.numel(), hi.data_ptr(),
+                                                                  lo.data_ptr(), _stream()), "split_tf32")
+            LAUNCHES[0] += 1
+            self.core_split = (hi, lo)
 
     def long_rows(self):
         """Number of rows the plan routes to the block-per-row kernel (synchronises)."""
@@ -275,7 +284,7 @@ def spmm(block, B, C, beta=1.0):
     use_core = block.core is not None and f >= CORE["min_width"] and ldb % 4 == 0 and B.data_ptr() % 16 == 0
     cores, src = [], block
     while use_core and src.core is not None:
-        cores.append(src.core)
+        cores.append(src.core + (src.core_split,))
         src = src.rest
     with _on(C.device):
         _native.check(_native.lib().cagnet_spmm_csr_f32(
@@ -283,29 +292,31 @@ def spmm(block, B, C, beta=1.0):
             B.data_ptr(), ldb, C.data_ptr(), ldc, f, float(beta),
             None if src.plan is None else src.plan.data_ptr(), _stream()), "spmm")
         LAUNCHES[0] += 1 if src.plan is None else 2
-        for dense, core_rows, core_cols in cores:
-            _core_multiply(dense, core_rows, core_cols, B, ldb, C, ldc, f)
+        for dense, core_rows, core_cols, split in cores:
+            _core_multiply(dense, core_rows, core_cols, split, B, ldb, C, ldc, f)
     return C
 
 
-def _core_multiply(dense, core_rows, core_cols, B, ldb, C, ldc, f):
+def _core_multiply(dense, core_rows, core_cols, split, B, ldb, C, ldc, f):
     """C[core_rows] += dense @ B[core_cols] on the current stream (device already current)."""
     L = _native.lib()
     r, k = dense.size(0), dense.size(1)
-    if core_on_tensor_cores() and dense.stride(0) % 4 == 0:
-        # tensor-core path: B's hub rows as one contiguous matrix (TMA cannot follow an index list), the
-        # product into a scratch matrix, its rows added into C's hub rows
-        Bs, D = empty_padded(k, f, C.device), empty_padded(r, f, C.device)
-        _native.check(L.cagnet_gather_rows_f32(B.data_ptr(), ldb, core_cols.data_ptr(), k, f, Bs.data_ptr(),
-                                               Bs.stride(0), _stream()), "gather_rows")
+    if split is not None and CORE["tensor_cores"]:
+        # tensor-core path (3xTF32): B's hub rows gathered and split into [hi | lo] (TMA cannot follow an index
+        # list), the three partial products into a scratch matrix, their sum added into C's hub rows
+        hi, lo = split
+        half = (f + 3) // 4 * 4
+        Bs = torch.empty(k * 2 * half, dtype=torch.float32, device=C.device)
+        D = torch.empty(r * 3 * half, dtype=torch.float32, device=C.device)
+        _native.check(L.cagnet_gather_split_rows_f32(B.data_ptr(), ldb, core_cols.data_ptr(), k, f, Bs.data_ptr(), half,
+                                                     _stream()), "gather_split_rows")
         nbytes = L.cagnet_core_gemm_tc_workspace_bytes(r, k, f)
         ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=C.device)
-        _native.check(L.cagnet_core_gemm_tc_f32(dense.data_ptr(), dense.stride(0), r, k, Bs.data_ptr(), Bs.stride(0),
-                                                D.data_ptr(), D.stride(0), f, ws.data_ptr(), ws.numel(), _stream()),
-                      "core_gemm_tc")
-        _native.check(L.cagnet_add_rows_f32(D.data_ptr(), D.stride(0), core_rows.data_ptr(), r, f, C.data_ptr(), ldc,
-                                            _stream()), "add_rows")
-        LAUNCHES[0] += 3
+        _native.check(L.cagnet_core_gemm_tc_f32(hi.data_ptr(), lo.data_ptr(), hi.stride(0), r, k, Bs.data_ptr(), half,
+                                                D.data_ptr(), f, ws.data_ptr(), ws.numel(), _stream()), "core_gemm_tc")
+        _native.check(L.cagnet_add_rows3_f32(D.data_ptr(), half, core_rows.data_ptr(), r, f, C.data_ptr(), ldc,
+                                             _stream()), "add_rows3")
+        LAUNCHES[0] += 2 + 2 * ((k + 2047) // 2048)
         return
     nbytes = L.cagnet_core_gemm_workspace_bytes(r, k, f)
     ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=C.device)

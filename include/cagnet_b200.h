@@ -117,21 +117,29 @@ int cagnet_core_gemm_f32(const float* core, int64_t ld_core, const int32_t* core
                          const float* B, int64_t ldb, float* C, int64_t ldc, int32_t f,
                          void* ws, size_t ws_bytes, void* stream);
 
-/* ---- The same dense core on the tensor cores: D[R x f] = core[R x K] * Bs[K x f], fp32 operands split into
- * three bf16 terms each inside the kernel (nine tcgen05 products per k block, fp32 promotion of the accumulator
- * after every k block: fp32-level accuracy).  Bs is the contiguous copy of the hub columns' rows of B
- * (cagnet_gather_rows_f32: out[k] = B[idx[k]]); D is added into the hub rows of C afterwards
- * (cagnet_add_rows_f32: C[rows[i]] += D[i]).  All rows 16-byte aligned, leading dimensions multiples of 4.
- * cagnet_core_gemm_tc_available() is 0 when the library was built without the CUTLASS header tree; the
- * multiply then returns CAGNET_E_ARG.  No counterpart in the reference. */
+/* ---- The same dense core on the tensor cores (tcgen05, kind::tf32) with fp32 accuracy ("3xTF32"): operands are
+ * split into hi (rounded to TF32) + lo (exact remainder) and core*Bs ~ hi*hi + (hi*lo + lo*hi).
+ *   cagnet_split_tf32_f32            hi[i], lo[i] of x[i]; run once on the core when the block is planned.
+ *   cagnet_gather_split_rows_f32     out[k] = [hi(B[idx[k]]) | lo(B[idx[k]])], K rows of 2*half floats, half >= f
+ *                                    rounded up to a multiple of 4 (columns [f, half) of both halves zeroed).
+ *   cagnet_core_gemm_tc_f32          D[R x 3*half]: columns [0, half) = core_hi*Bs_hi, [half, 2 half) =
+ *                                    core_hi*Bs_lo, [2 half, 3 half) = core_lo*Bs_hi; the k range is cut into
+ *                                    chunks whose sums are added in fp32 (a tensor-core accumulator over the whole
+ *                                    k range loses about 3e-5 at k = 13K).  ws: cagnet_core_gemm_tc_workspace_bytes.
+ *   cagnet_add_rows3_f32             C[rows[i], n] += D[i, n] + (D[i, half+n] + D[i, 2 half+n]), n < f.
+ * All row starts 16-byte aligned.  cagnet_core_gemm_tc_available() is 0 when the library was built without the
+ * CUTLASS header tree; the multiply then returns CAGNET_E_ARG (the three small kernels work regardless).
+ * No counterpart in the reference. */
 int cagnet_core_gemm_tc_available(void);
 size_t cagnet_core_gemm_tc_workspace_bytes(int32_t R, int32_t K, int32_t f);
-int cagnet_core_gemm_tc_f32(const float* core, int64_t ld_core, int32_t R, int32_t K, const float* Bs, int64_t ldbs,
-                            float* D, int64_t ldd, int32_t f, void* ws, size_t ws_bytes, void* stream);
-int cagnet_gather_rows_f32(const float* B, int64_t ldb, const int32_t* idx, int32_t K, int32_t f, float* out,
-                           int64_t ldo, void* stream);
-int cagnet_add_rows_f32(const float* D, int64_t ldd, const int32_t* rows, int32_t R, int32_t f, float* C,
-                        int64_t ldc, void* stream);
+int cagnet_split_tf32_f32(const float* x, int64_t count, float* hi, float* lo, void* stream);
+int cagnet_gather_split_rows_f32(const float* B, int64_t ldb, const int32_t* idx, int32_t K, int32_t f, float* out,
+                                 int64_t half, void* stream);
+int cagnet_core_gemm_tc_f32(const float* core_hi, const float* core_lo, int64_t ld_core, int32_t R, int32_t K,
+                            const float* Bs, int64_t half, float* D, int32_t f, void* ws, size_t ws_bytes,
+                            void* stream);
+int cagnet_add_rows3_f32(const float* D, int64_t half, const int32_t* rows, int32_t R, int32_t f, float* C,
+                         int64_t ldc, void* stream);
 
 /* ---- Z = epilogue(X * W) for a tall X (n x K, ldx) and a small W.
  * transW = 0: W is K x N row-major (ldw);  transW = 1: W is N x K row-major (ldw) and is used
