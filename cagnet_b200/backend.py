@@ -99,9 +99,11 @@ class CudaBackend:
     def wire_buffer(self, n, nnz):
         return torch.empty(n + 1 + 2 * nnz, dtype=torch.int32, device=self.device)
 
-    def block_from_wire(self, buf, n, m, nnz):
+    def block_from_wire(self, buf, n, m, nnz, reused=False):
+        """A received block.  `reused`: the caller keeps it across epochs, so the one-off search for a dense core
+        pays; a block that lives for one multiply only gets its hub-row list."""
         blk = ops.CsrBlock(buf[:n + 1], buf[n + 1:n + 1 + nnz], buf[n + 1 + nnz:].view(torch.float32), n, m)
-        blk.build_plan()
+        blk.build_plan(core=bool(reused))
         return blk
 
     # ---- row-wise pieces of a log-softmax split by columns over a process row

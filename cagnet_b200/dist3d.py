@@ -98,7 +98,7 @@ def split3dspmm_sparse(model, inputs):
         with rt.timers.region("comm_time", "summa_sparse_bcast1"):
             _bcast(buf, src, g.row_group)
         rt.timers.count("summa_sparse_bcast1_words", buf.numel())
-        blk = be.block_from_wire(buf, n_r, n_c, nnz)
+        blk = be.block_from_wire(buf, n_r, n_c, nnz, reused=rt.cache_blocks)
         if rt.cache_blocks:
             model.block_cache[kp] = blk
         return blk

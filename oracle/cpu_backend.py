@@ -33,7 +33,7 @@ class CpuBackend:
     def wire_buffer(self, n, nnz):
         return torch.zeros(n + 1 + 2 * nnz, dtype=torch.int32)
 
-    def block_from_wire(self, buf, n, m, nnz):
+    def block_from_wire(self, buf, n, m, nnz, reused=False):
         rowptr = buf[:n + 1].long()
         rows = torch.repeat_interleave(torch.arange(n), rowptr[1:] - rowptr[:-1])
         return _CpuBlock(rows, buf[n + 1:n + 1 + nnz], buf[n + 1 + nnz:].clone().view(torch.float32), n, m)
