@@ -2,8 +2,9 @@
 
 Mirrors the reference's native operator surface (`sparse_coo_tensor_cpp.spmm_gpu`,
 `sparse_coo_tensor_cpp.sparse_coo_tensor_gpu`; sparse-extension/sparse_coo_tensor.cu:43-54, 113-240)
-and adds the cached-CSR form the GCN layers use.  PyTorch is only the owner of device memory and
-streams here; every computation is a kernel of `libcagnet_b200.so`.  CPU tensors are rejected.
+and adds the cached-CSR form the GCN layers use.  PyTorch is the owner of device memory and streams
+here; every multiply, activation and loss is a kernel of `libcagnet_b200.so` (torch index kernels are used
+once per block, when its dense core is looked for and cut out).  CPU tensors are rejected.
 """
 import os
 
