@@ -52,6 +52,31 @@ def test_argument_errors_are_status_codes_not_crashes():
     assert lib.cagnet_coo2csr_i32(1, 2 ** 31, 3, 1, None) == 3
 
 
+def test_dense_core_entry_points_validate_before_launching():
+    lib = _native.lib()
+    p = 0x7f0000000000                      # never dereferenced: every call below fails its argument checks
+    assert lib.cagnet_core_gemm_workspace_bytes(0, 10, 10) == 0
+    assert lib.cagnet_core_gemm_workspace_bytes(4096, 13312, 602) >= 4096 * 604 * 4
+    assert lib.cagnet_core_gemm_f32(p, 8, p, -1, p, 8, p, 8, p, 8, 8, None, 0, None) == 1
+    assert lib.cagnet_core_gemm_f32(p, 4, p, 8, p, 8, p, 8, p, 8, 8, None, 0, None) == 1        # ld_core < K
+    assert lib.cagnet_core_gemm_f32(p, 8, p, 8, p, 8, p, 7, p, 8, 7, None, 0, None) == 2        # B rows unaligned
+    assert lib.cagnet_core_gemm_f32(p, 13312, p, 4096, p, 13312, p, 608, p, 608, 602, None, 0, None) == 5   # no scratch
+    assert lib.cagnet_core_gemm_f32(p, 8, p, 0, p, 8, p, 8, p, 8, 8, None, 0, None) == 0        # nothing to do
+    assert lib.cagnet_split_tf32_f32(None, 0, None, None, None) == 0
+    assert lib.cagnet_split_tf32_f32(None, 5, None, None, None) == 1
+    assert lib.cagnet_gather_split_rows_f32(p, 6, p, 4, 6, p, 8, None) == 2                     # ldb not a multiple of 4
+    assert lib.cagnet_gather_split_rows_f32(p, 8, p, 4, 6, p, 4, None) == 2                     # half < f rounded up
+    assert lib.cagnet_add_rows3_f32(p, 6, p, 4, 6, p, 8, None) == 2
+    assert lib.cagnet_add_rows3_f32(p, 8, p, 4, 6, p, 4, None) == 2                             # ldc < f
+    assert lib.cagnet_core_gemm_tc_available() in (0, 1)
+    if lib.cagnet_core_gemm_tc_available():
+        assert lib.cagnet_core_gemm_tc_workspace_bytes(4096, 4096, 602) >= 16
+        assert lib.cagnet_core_gemm_tc_f32(p, p, 8, 4, 16, p, 8, p, 8, None, 0, None) == 1      # ld_core < K
+        assert lib.cagnet_core_gemm_tc_f32(p, p, 18, 4, 16, p, 8, p, 8, None, 0, None) == 2     # ld_core % 4
+    else:
+        assert lib.cagnet_core_gemm_tc_f32(p, p, 16, 4, 16, p, 8, p, 8, None, 0, None) == 1
+
+
 def test_cpu_tensors_are_refused():
     blk = ops.CsrBlock(torch.zeros(3, dtype=torch.int32), torch.zeros(0, dtype=torch.int32), torch.zeros(0), 2, 2)
     with pytest.raises(RuntimeError, match="CUDA tensor"):
