@@ -132,7 +132,8 @@ def _row_major(t):
 # multiplying densely when more than this share of its cells are nonzeros (gathering one 2.4 KB row of B per
 # nonzero costs about five dense cells at width 602); "step": side lengths tried are multiples of this;
 # "max_side" / "max_bytes": limits of the rectangle; "min_share": the rectangle must save at least this share of
-# the block's nonzero-gathers to be cut out; "min_width": products narrower than this keep using the full CSR
+# the block's nonzero-gathers to be cut out (the gathers a core removes are the cheap ones, rows of B that live in
+# L2: on edge-factor-16 R-MAT graphs, whose cost is the DRAM-bound rest, cores worth 4-5 % measured -2 % .. +10 %); "min_width": products narrower than this keep using the full CSR
 # block (they are bound per nonzero, not per byte, and a 128-column dense tile would be mostly padding); "rounds":
 # how many rectangles may be cut out one after the other (a second one, 9,216 x 4,096 at 30 % density on the
 # benchmark graph, measured no gain: 13.30 ms against 13.13 ms).
@@ -140,7 +141,7 @@ def _row_major(t):
 # through a three-term bf16 split, 123 TFLOP/s against 40 for the fp32-FMA kernel); a dense cell then costs a
 # twelfth of a gathered nonzero and "density_tc" is the bar instead of "density".
 CORE = {"enabled": os.environ.get("CAGNET_DENSE_CORE", "1") != "0", "density": 0.2, "density_tc": 0.09, "step": 1024,
-        "max_side": 16384, "max_bytes": 2 << 30, "min_share": 0.03, "min_width": 128, "rounds": 1,
+        "max_side": 16384, "max_bytes": 2 << 30, "min_share": 0.1, "min_width": 128, "rounds": 1,
         "tensor_cores": os.environ.get("CAGNET_CORE_TENSOR", "1") != "0"}
 
 

@@ -75,7 +75,10 @@ def main(argv=None):
             alg = A.bytes_alg(f, 0.0)
             rec = {"scale": scale, "vertices": n, "nnz": A.nnz, "f": f, "ms": ms, "alg_gbs": alg / ms / 1e6,
                    "frac_of_hbm_peak": alg / ms / 1e6 / peak, "peak_gbs": peak, "peak_source": peak_kind,
-                   "gather_gbs": (8 * A.nnz + 4 * A.nnz * f) / ms / 1e6, "hub_rows": A.long_rows(), "cpu_ms": None,
+                   "gather_gbs": (8 * A.nnz + 4 * A.nnz * f) / ms / 1e6, "hub_rows": A.long_rows(),
+                   "dense_core": None if A.core is None else [int(A.core[0].size(0)), int(A.core[0].size(1)),
+                                                               A.nnz - A.rest.nnz],
+                   "dense_core_used": A.core is not None and f >= ops.CORE["min_width"], "cpu_ms": None,
                    "cpu_threads": None}
             if cpu_mat is not None:
                 flops = 2.0 * A.nnz * f
