@@ -30,4 +30,8 @@ __host__ __device__ inline bool aligned(const void* p, size_t a) { return (reint
 
 constexpr int kNumSMs = 148;  // B200
 
+// k length of one tensor-core accumulation of the dense-core multiply (tuning knob "core_chunk")
+int core_chunk();
+int set_core_chunk(int value);
+
 }  // namespace cagnet

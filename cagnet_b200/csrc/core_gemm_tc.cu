@@ -12,7 +12,7 @@
 //
 // Accuracy: a tensor-core accumulator is not a round-to-nearest fp32 sum, and its error grows with the length of
 // the contraction (measured 2.8e-5 of the largest magnitude at k = 13,312 in one piece).  The k range is
-// therefore cut into chunks of kChunk; each chunk's GEMM adds into D in its epilogue (beta = 1), which is a
+// therefore cut into chunks (tuning knob "core_chunk", 2,048 by default); each chunk's GEMM adds into D in its epilogue (beta = 1), which is a
 // proper fp32 addition.
 //
 // This file instantiates CUTLASS / CuTe templates (header tree found at build time) and adds the split kernels
@@ -85,6 +85,14 @@ add_rows3_kernel(const float* __restrict__ D, int64_t half, const int* __restric
   if (n + 3 < f) out[3] += a.w + (b.w + c.w);
 }
 
+static int g_core_chunk = 2048;
+int core_chunk() { return g_core_chunk; }
+int set_core_chunk(int value) {
+  if (value < 256 || value % 32) return 1;
+  g_core_chunk = value;
+  return 0;
+}
+
 }  // namespace cagnet
 
 #ifdef CAGNET_HAVE_CUTLASS
@@ -127,7 +135,6 @@ using Mainloop = typename cutlass::gemm::collective::CollectiveBuilder<
 using Kernel = cutlass::gemm::kernel::GemmUniversal<Shape<int, int, int, int>, Mainloop, Epilogue>;
 using Gemm = cutlass::gemm::device::GemmUniversalAdapter<Kernel>;
 
-constexpr int kChunk = 2048;                    // k length of one tensor-core accumulation
 
 static typename Gemm::Arguments make_args(const float* A, int64_t lda, const float* B, int64_t ldb, float* D,
                                           int64_t ldd, int M, int N, int K, float beta) {
@@ -176,7 +183,7 @@ extern "C" int cagnet_core_gemm_tc_available(void) { return 1; }
 extern "C" size_t cagnet_core_gemm_tc_workspace_bytes(int32_t R, int32_t K, int32_t f) {
   if (R <= 0 || K <= 0 || f <= 0) return 0;
   const int half = (f + 3) / 4 * 4;
-  auto args = tc::make_args(nullptr, K, nullptr, 2 * half, nullptr, 3 * half, R, 2 * half, K < tc::kChunk ? K : tc::kChunk, 0.f);
+  auto args = tc::make_args(nullptr, K, nullptr, 2 * half, nullptr, 3 * half, R, 2 * half, K < core_chunk() ? K : core_chunk(), 0.f);
   return tc::Gemm::get_workspace_size(args) + 16;
 }
 
@@ -191,8 +198,9 @@ extern "C" int cagnet_core_gemm_tc_f32(const float* core_hi, const float* core_l
     return fail(CAGNET_E_ALIGN, "cagnet_core_gemm_tc_f32: rows of the core, Bs and D must start on 16-byte boundaries");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int n1 = static_cast<int>(2 * half), n2 = static_cast<int>(half);
-  for (int k0 = 0; k0 < K; k0 += tc::kChunk) {
-    const int kc = (K - k0 < tc::kChunk) ? K - k0 : tc::kChunk;
+  const int chunk = core_chunk();
+  for (int k0 = 0; k0 < K; k0 += chunk) {
+    const int kc = (K - k0 < chunk) ? K - k0 : chunk;
     const float beta = k0 == 0 ? 0.f : 1.f;
     const float* b = Bs + static_cast<int64_t>(k0) * 2 * half;
     // D[:, 0:2 half) (+)= core_hi[:, k0:k0+kc) * [Bs_hi | Bs_lo][k0:k0+kc)

@@ -363,6 +363,10 @@ extern "C" int cagnet_set_param(const char* name, int value) {
     g_tuning.spmm_rpb = value;
     return CAGNET_OK;
   }
+  if (!strcmp(name, "core_chunk")) {
+    if (set_core_chunk(value)) return fail(CAGNET_E_ARG, "cagnet_set_param: core_chunk must be a multiple of 32, >= 256");
+    return CAGNET_OK;
+  }
   if (!strcmp(name, "spmm_long_narrow")) {
     if (value < kMinLongThreshold) return fail(CAGNET_E_ARG, "cagnet_set_param: spmm_long_narrow must be >= 256");
     g_tuning.spmm_long_narrow = value;
@@ -381,6 +385,7 @@ extern "C" int cagnet_get_param(const char* name) {
   if (name && !strcmp(name, "spmm_rpb")) return g_tuning.spmm_rpb;
   if (name && !strcmp(name, "spmm_long")) return g_tuning.spmm_long;
   if (name && !strcmp(name, "spmm_long_narrow")) return g_tuning.spmm_long_narrow;
+  if (name && !strcmp(name, "core_chunk")) return core_chunk();
   return -1;
 }
 

@@ -318,7 +318,8 @@ def _core_multiply(dense, core_rows, core_cols, split, B, ldb, C, ldc, f):
                                                 D.data_ptr(), f, ws.data_ptr(), ws.numel(), _stream()), "core_gemm_tc")
         _native.check(L.cagnet_add_rows3_f32(D.data_ptr(), half, core_rows.data_ptr(), r, f, C.data_ptr(), ldc,
                                              _stream()), "add_rows3")
-        LAUNCHES[0] += 2 + 2 * ((k + 2047) // 2048)
+        chunk = _native.get_param("core_chunk")
+        LAUNCHES[0] += 2 + 2 * ((k + chunk - 1) // chunk)
         return
     nbytes = L.cagnet_core_gemm_workspace_bytes(r, k, f)
     ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=C.device)

@@ -46,7 +46,8 @@ const char* cagnet_last_error_string(void);
  * two-vectors-per-lane mapping for products of 5..16 vectors), "spmm_rpb" (rows per thread block of the
  * warp-per-row kernel), "spmm_long" (rows with more nonzeros than this are listed in the plan and processed by a
  * whole thread block), "spmm_long_narrow" (a lower bound on that limit for products narrower than 128 columns;
- * equal to "spmm_long" by default).  Host-side global state; returns CAGNET_E_ARG for an unknown name or value. */
+ * equal to "spmm_long" by default), "core_chunk" (k length of one tensor-core accumulation of the dense-core
+ * multiply, a multiple of 32).  Host-side global state; returns CAGNET_E_ARG for an unknown name or value. */
 int cagnet_set_param(const char* name, int value);
 int cagnet_get_param(const char* name);
 
