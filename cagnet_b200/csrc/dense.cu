@@ -224,6 +224,124 @@ __global__ void __launch_bounds__(256) gemm_tn_partial_kernel(const float* __res
   }
 }
 
+// The same product for N <= 16 (the weight gradients of the 602 x 16 layer: H is the 233K x 602 feature matrix,
+// G has 16 columns).  There the kernel above spends two shared-memory reads on four FMAs, prefetches one step
+// ahead and runs at 1.4 TB/s of H with its warps waiting on the loads.  Here
+//   * a thread owns 4 consecutive k and all 16 columns (64 accumulators) for one sixteenth of the rows of a step:
+//     one 128-bit read of H and four of G feed 64 FMAs;
+//   * the tiles of the next three steps are already on their way: 16-byte cp.async copies into a four-stage ring
+//     of shared-memory tiles (64 rows x 64 columns of H and 64 x 16 of G per stage), out-of-range rows and
+//     columns zero-filled by the copy's source size.
+// Threads that share their k columns (same tid % 16) are summed at the end, first by a shuffle inside each warp,
+// then over the 8 warps in warp order.  Needs 16-byte aligned rows of H and G.
+constexpr int kTnSmallRB = 64;       // rows per step
+constexpr int kTnSmallStages = 4;
+constexpr int kTnSmallStageFloats = kTnSmallRB * kTnKT + kTnSmallRB * 16;
+constexpr int kTnSmallSmemBytes = kTnSmallStages * kTnSmallStageFloats * 4;     // 80 KB; also holds the 32 KB of sums
+
+__device__ __forceinline__ void cp_async16(float* smem_dst, const float* gmem_src, int src_bytes) {
+  const unsigned dst = static_cast<unsigned>(__cvta_generic_to_shared(smem_dst));
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(gmem_src), "r"(src_bytes) : "memory");
+}
+
+__global__ void __launch_bounds__(256, 2) gemm_tn_small_kernel(const float* __restrict__ H, int64_t ldh,
+                                                               const float* __restrict__ G, int64_t ldg, int64_t n,
+                                                               int K, int N, int64_t rows_per_chunk,
+                                                               float* __restrict__ ws) {
+  extern __shared__ __align__(16) float tn_smem[];
+  const int tid = threadIdx.x;
+  const int kq = tid & 15, rs = tid >> 4;
+  const int k0 = blockIdx.y * kTnKT;
+  const int64_t r_begin = static_cast<int64_t>(blockIdx.x) * rows_per_chunk;
+  const int64_t r_end = min(n, r_begin + rows_per_chunk);
+  const int steps = static_cast<int>((r_end - r_begin + kTnSmallRB - 1) / kTnSmallRB);
+
+  // copies of one step: 4 float4 of H and 1 float4 of G per thread
+  auto issue = [&](int step) {
+    if (step < steps) {
+      float* hs = tn_smem + (step % kTnSmallStages) * kTnSmallStageFloats;
+      float* gs = hs + kTnSmallRB * kTnKT;
+      const int64_t r0 = r_begin + static_cast<int64_t>(step) * kTnSmallRB;
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int idx = tid + 256 * u;             // float4 index in the H tile
+        const int r = idx >> 4, c = (idx & 15) * 4;
+        const int k = k0 + c;
+        int bytes = (r0 + r < r_end) ? (K - k) * 4 : 0;
+        bytes = bytes < 0 ? 0 : (bytes > 16 ? 16 : bytes);
+        const float* src = bytes ? H + (r0 + r) * ldh + k : H;
+        cp_async16(hs + r * kTnKT + c, src, bytes);
+      }
+      const int r = tid >> 2, j = (tid & 3) * 4;
+      int bytes = (r0 + r < r_end) ? (N - j) * 4 : 0;
+      bytes = bytes < 0 ? 0 : (bytes > 16 ? 16 : bytes);
+      const float* src = bytes ? G + (r0 + r) * ldg + j : G;
+      cp_async16(gs + r * 16 + j, src, bytes);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");     // an empty group keeps the count in step
+  };
+
+  float acc[4][16];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 16; ++j) acc[i][j] = 0.f;
+
+#pragma unroll
+  for (int s = 0; s < kTnSmallStages - 1; ++s) issue(s);
+  for (int step = 0; step < steps; ++step) {
+    asm volatile("cp.async.wait_group %0;" ::"n"(kTnSmallStages - 2) : "memory");   // this step's tiles have landed
+    __syncthreads();                     // ... for every thread, and everyone is done with the stage refilled next
+    issue(step + kTnSmallStages - 1);
+    const float* hs = tn_smem + (step % kTnSmallStages) * kTnSmallStageFloats;
+    const float* gs = hs + kTnSmallRB * kTnKT;
+#pragma unroll
+    for (int q = 0; q < kTnSmallRB / 16; ++q) {
+      const int r = rs + 16 * q;
+      const float4 h4 = *reinterpret_cast<const float4*>(hs + r * kTnKT + kq * 4);
+      const float h[4] = {h4.x, h4.y, h4.z, h4.w};
+      float g[16];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const float4 g4 = *reinterpret_cast<const float4*>(gs + r * 16 + c * 4);
+        g[4 * c + 0] = g4.x; g[4 * c + 1] = g4.y; g[4 * c + 2] = g4.z; g[4 * c + 3] = g4.w;
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 16; ++j) acc[i][j] = fmaf(h[i], g[j], acc[i][j]);
+    }
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  __syncthreads();                       // the ring is free: it now holds the partial sums of the 8 warps
+  float (*red)[16][64] = reinterpret_cast<float (*)[16][64]>(tn_smem);
+  // lanes l and l + 16 of a warp hold the same k columns for two row subsets
+  const int warp = tid >> 5, lane = tid & 31;
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 16; ++j) acc[i][j] += __shfl_down_sync(0xffffffffu, acc[i][j], 16);
+  if (lane < 16) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 16; j += 4)
+        *reinterpret_cast<float4*>(&red[warp][lane][i * 16 + j]) =
+            make_float4(acc[i][j], acc[i][j + 1], acc[i][j + 2], acc[i][j + 3]);
+  }
+  __syncthreads();
+  float* wp = ws + static_cast<int64_t>(blockIdx.x) * K * N;
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    const int e = tid + 256 * u;                  // element of the 64 x 16 tile: k = e / 16, column j = e % 16
+    const int kk = e >> 4, j = e & 15;
+    float sum = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) sum += red[w][kk >> 2][(kk & 3) * 16 + j];
+    if (k0 + kk < K && j < N) wp[static_cast<int64_t>(k0 + kk) * N + j] = sum;
+  }
+}
+
 __global__ void gemm_tn_reduce_kernel(const float* __restrict__ ws, int chunks, int K, int N, float* __restrict__ out,
                                       int64_t ldo, float beta) {
   const int idx = blockIdx.x * blockDim.x + threadIdx.x;
@@ -454,8 +572,24 @@ extern "C" int cagnet_gemm_tn_f32(const float* H, int64_t ldh, const float* G, i
                 (long long)ws_bytes, (long long)cagnet_gemm_tn_workspace_bytes(n, K, N));
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const TnShape sh = tn_shape(n, K, N);
-  gemm_tn_partial_kernel<<<dim3(sh.chunks, sh.ktiles, sh.ntiles), 256, 0, s>>>(H, ldh, G, ldg, n, K, N, sh.rows_per_chunk,
-                                                                              static_cast<float*>(ws));
+  if (N <= 16 && ldh % 4 == 0 && ldg % 4 == 0 && aligned(H, 16) && aligned(G, 16)) {
+    // 80 KB of dynamic shared memory: opt in once per device
+    static bool opted_in[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !opted_in[dev]) {
+      if (cudaFuncSetAttribute(gemm_tn_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTnSmallSmemBytes) !=
+          cudaSuccess)
+        return fail(CAGNET_E_LAUNCH, "cagnet_gemm_tn_f32: cannot reserve shared memory for the small-N kernel");
+      opted_in[dev] = true;
+    }
+    gemm_tn_small_kernel<<<dim3(sh.chunks, sh.ktiles), 256, kTnSmallSmemBytes, s>>>(H, ldh, G, ldg, n, K, N,
+                                                                                   sh.rows_per_chunk,
+                                                                                   static_cast<float*>(ws));
+  } else {
+    gemm_tn_partial_kernel<<<dim3(sh.chunks, sh.ktiles, sh.ntiles), 256, 0, s>>>(H, ldh, G, ldg, n, K, N,
+                                                                                sh.rows_per_chunk, static_cast<float*>(ws));
+  }
   gemm_tn_reduce_kernel<<<(K * N + 255) / 256, 256, 0, s>>>(static_cast<const float*>(ws), sh.chunks, K, N, out, ldo, beta);
   return check_launch("cagnet_gemm_tn_f32");
 }
