@@ -41,6 +41,17 @@ def measured_peak_gbs():
         return 6650.0, "fallback"
 
 
+def dense_core_info(model):
+    """What rank 0's first adjacency block was split into (rows x columns of the dense core, its nonzeros, and
+    whether it is multiplied on the tensor cores), or None when the block is all-sparse."""
+    blk = model.am_pbyp.groups[0].block if model.am_pbyp.groups else None
+    if blk is None or blk.core is None:
+        return None
+    dense = blk.core[0]
+    return {"rows": int(dense.size(0)), "cols": int(dense.size(1)), "nnz": int(blk.nnz - blk.rest.nnz),
+            "tensor_cores": blk.core_split is not None}
+
+
 def spmm_traffic_bytes():
     """DRAM bytes per launch of the dominant SpMM from the committed ncu summary, or None."""
     try:
@@ -300,6 +311,7 @@ def run_ours(args):
             "gpu_launches": launches, "clocks": clocks, "loss": loss_resident, "loss_e2e": loss_host,
             "multiplication_order": args.order, "stage_groups": args.stage_groups, "collective": args.collective,
             "alt_order": alt,
+            "dense_core": dense_core_info(model),
         }
         if world == 1:
             M, X, y, mask = build_cpu_problem(model, y_all, mask_all)
