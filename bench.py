@@ -44,12 +44,15 @@ def measured_peak_gbs():
 def dense_core_info(model):
     """What rank 0's first adjacency block was split into (rows x columns of the dense core, its nonzeros, and
     whether it is multiplied on the tensor cores), or None when the block is all-sparse."""
-    blk = model.am_pbyp.groups[0].block if model.am_pbyp.groups else None
-    if blk is None or blk.core is None:
+    try:
+        blk = model.am_pbyp.groups[0].block
+        if blk.core is None:
+            return None
+        dense = blk.core[0]
+        return {"rows": int(dense.size(0)), "cols": int(dense.size(1)), "nnz": int(blk.nnz - blk.rest.nnz),
+                "tensor_cores": blk.core_split is not None}
+    except (AttributeError, IndexError):      # an informational field must not cost the line
         return None
-    dense = blk.core[0]
-    return {"rows": int(dense.size(0)), "cols": int(dense.size(1)), "nnz": int(blk.nnz - blk.rest.nnz),
-            "tensor_cores": blk.core_split is not None}
 
 
 def spmm_traffic_bytes():
