@@ -69,3 +69,23 @@ def test_no_rectangle_in_a_uniform_block_and_limits():
     assert big.r * big.c > 64 * 64 >= small.r * small.c
     empty = torch.zeros(0, dtype=torch.int64)
     assert core_select.choose_core(torch.zeros(11, dtype=torch.int32), empty, 10, 10, 0.2, step=2) is None
+
+
+def test_rectangular_block_of_a_block_row():
+    """A rank's block row (fewer rows than columns): rows and columns are ranked separately."""
+    n = 512
+    b, _ = _block(n, seed=6)
+    lo, hi = 128, 384                                  # rows [128, 384) of the graph, all columns
+    sel = (b.rows >= lo) & (b.rows < hi)
+    rows, cols, vals = b.rows[sel] - lo, b.cols[sel], b.vals[sel]
+    rowptr = torch.from_numpy(OG.coo2csr(rows.int().numpy(), hi - lo))
+    ch = core_select.choose_core(rowptr, cols, hi - lo, n, 0.15, step=16, max_side=256, min_share=0.0)
+    assert ch is not None and ch.r <= hi - lo and ch.c <= 256
+    assert int(ch.rows.max()) < hi - lo and int(ch.cols.max()) < n
+    dense, rest_rowptr, rest_col, rest_val = core_select.split_core(cols, vals, hi - lo, ch)
+    full = torch.zeros(hi - lo, n)
+    rest_rows = torch.repeat_interleave(torch.arange(hi - lo), (rest_rowptr[1:] - rest_rowptr[:-1]).long())
+    full[rest_rows, rest_col.long()] = rest_val
+    full[ch.rows[:, None], ch.cols[None, :]] += dense
+    want = torch.sparse_coo_tensor(torch.stack([rows, cols]), vals, (hi - lo, n)).to_dense()
+    assert torch.equal(full, want)
