@@ -33,7 +33,7 @@ def cutlass_include_dirs():
         spec = None
     for root in (list(spec.submodule_search_locations) if spec and spec.submodule_search_locations else []):
         inc = os.path.join(root, "data", "cutlass", "include")
-        if os.path.exists(os.path.join(inc, "cutlass", "gemm", "collective", "builders", "sm100_9xBF16_umma_builder.inl")):
+        if os.path.exists(os.path.join(inc, "cutlass", "gemm", "collective", "builders", "sm100_umma_builder.inl")):
             return [inc, os.path.join(root, "data", "cutlass", "tools", "util", "include")]
     return []
 
