@@ -350,10 +350,11 @@ class Model:
         inputs_loc, blocks = partition.oned_partition(rank, size, inputs, adj_matrix, rt.normalization, c)
         self.inputs_loc = be.as_matrix(inputs_loc)
         n_per_proc = int(math.ceil(float(node_count) / (size / c)))
-        # automatic launch groups: two (communication of the second under the multiply of the first) up to 4
-        # ranks, one beyond -- the per-rank multiply shrinks as 1/P while the cost of a launch does not, and on the
-        # 233K-vertex benchmark graph the crossover lies between 4 and 8 ranks (6.8 ms against 7.6 ms per epoch at 8)
-        groups = rt.stage_groups if rt.stage_groups >= 0 else (2 if size <= 4 else 1)
+        # automatic launch groups: one.  Two groups put the communication of the second under the multiply of the
+        # first, but every group is a block of its own: its dense core is smaller and multiplies less efficiently,
+        # and each launch costs the same however little it does.  Measured on the 233K-vertex benchmark graph:
+        # 2 ranks 9.72 ms (one group) against 10.06 ms (two); 8 ranks 6.8 against 7.6 ms (before the dense core).
+        groups = rt.stage_groups if rt.stage_groups >= 0 else 1
         if c == 1 and size > 1 and rt.collective == "all_gather":
             self.am_pbyp = GatherPlan(be, blocks, rank, size, n_per_proc, groups)
         else:
