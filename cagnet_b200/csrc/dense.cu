@@ -347,7 +347,7 @@ __global__ void __launch_bounds__(256, 2) gemm_tn_small_kernel(const float* __re
 // on every run.  (One thread per element walking all chunks took 56 us for a 16 x 41 product cut into 561 chunks.)
 __global__ void __launch_bounds__(256)
 gemm_tn_reduce_kernel(const float* __restrict__ ws, int chunks, int K, int N, float* __restrict__ out, int64_t ldo,
-                      float beta) {
+                      float beta, int transposed) {
   const int idx = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;      // warp-uniform
   const int lane = threadIdx.x & 31;
   if (idx >= K * N) return;
@@ -356,7 +356,9 @@ gemm_tn_reduce_kernel(const float* __restrict__ ws, int chunks, int K, int N, fl
 #pragma unroll
   for (int off = 16; off > 0; off >>= 1) s += __shfl_down_sync(0xffffffffu, s, off);
   if (lane == 0) {
-    float* o = out + static_cast<int64_t>(idx / N) * ldo + idx % N;
+    // transposed: the partials are those of G^T * H (K and N as passed here); out is (H^T * G)[N x K]
+    float* o = transposed ? out + static_cast<int64_t>(idx % N) * ldo + idx / N
+                          : out + static_cast<int64_t>(idx / N) * ldo + idx % N;
     *o = (beta != 0.f) ? s + *o : s;
   }
 }
@@ -564,8 +566,22 @@ extern "C" int cagnet_gemm_nn_f32(const float* X, int64_t ldx, const float* W, i
 
 extern "C" size_t cagnet_gemm_tn_workspace_bytes(int64_t n, int32_t K, int32_t N) {
   if (n < 0 || K <= 0 || N <= 0) return 0;
-  const TnShape sh = tn_shape(n, K, N);
-  return sizeof(float) * static_cast<size_t>(sh.chunks) * K * N;
+  const int chunks = max(tn_shape(n, K, N).chunks, tn_shape(n, N, K).chunks);     // either operand order
+  return sizeof(float) * static_cast<size_t>(chunks) * K * N;
+}
+
+// The small-N kernel needs 80 KB of dynamic shared memory: opt in once per device.
+static int tn_small_opt_in() {
+  static bool opted_in[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !opted_in[dev]) {
+    if (cudaFuncSetAttribute(gemm_tn_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTnSmallSmemBytes) !=
+        cudaSuccess)
+      return fail(CAGNET_E_LAUNCH, "cagnet_gemm_tn_f32: cannot reserve shared memory for the small-N kernel");
+    opted_in[dev] = true;
+  }
+  return CAGNET_OK;
 }
 
 extern "C" int cagnet_gemm_tn_f32(const float* H, int64_t ldh, const float* G, int64_t ldg, float* out, int64_t ldo,
@@ -580,26 +596,28 @@ extern "C" int cagnet_gemm_tn_f32(const float* H, int64_t ldh, const float* G, i
     return fail(CAGNET_E_WORKSPACE, "cagnet_gemm_tn_f32: workspace of %s%lld bytes is too small (need %lld)", "",
                 (long long)ws_bytes, (long long)cagnet_gemm_tn_workspace_bytes(n, K, N));
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const TnShape sh = tn_shape(n, K, N);
-  if (N <= 16 && ldh % 4 == 0 && ldg % 4 == 0 && aligned(H, 16) && aligned(G, 16)) {
-    // 80 KB of dynamic shared memory: opt in once per device
-    static bool opted_in[64] = {};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !opted_in[dev]) {
-      if (cudaFuncSetAttribute(gemm_tn_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTnSmallSmemBytes) !=
-          cudaSuccess)
-        return fail(CAGNET_E_LAUNCH, "cagnet_gemm_tn_f32: cannot reserve shared memory for the small-N kernel");
-      opted_in[dev] = true;
-    }
+  float* partials = static_cast<float*>(ws);
+  const bool rows_aligned = ldh % 4 == 0 && ldg % 4 == 0 && aligned(H, 16) && aligned(G, 16);
+  if (N <= 16 && rows_aligned) {
+    const TnShape sh = tn_shape(n, K, N);
+    if (int rc = tn_small_opt_in()) return rc;
     gemm_tn_small_kernel<<<dim3(sh.chunks, sh.ktiles), 256, kTnSmallSmemBytes, s>>>(H, ldh, G, ldg, n, K, N,
-                                                                                   sh.rows_per_chunk,
-                                                                                   static_cast<float*>(ws));
+                                                                                   sh.rows_per_chunk, partials);
+    gemm_tn_reduce_kernel<<<(K * N + 7) / 8, 256, 0, s>>>(partials, sh.chunks, K, N, out, ldo, beta, 0);
+  } else if (K <= 16 && rows_aligned) {
+    // a narrow H against a wider G (the 16 x 41 weight gradient): the same kernel computes G^T * H, the reduce
+    // writes it transposed
+    const TnShape sh = tn_shape(n, N, K);
+    if (int rc = tn_small_opt_in()) return rc;
+    gemm_tn_small_kernel<<<dim3(sh.chunks, sh.ktiles), 256, kTnSmallSmemBytes, s>>>(G, ldg, H, ldh, n, N, K,
+                                                                                   sh.rows_per_chunk, partials);
+    gemm_tn_reduce_kernel<<<(K * N + 7) / 8, 256, 0, s>>>(partials, sh.chunks, N, K, out, ldo, beta, 1);
   } else {
+    const TnShape sh = tn_shape(n, K, N);
     gemm_tn_partial_kernel<<<dim3(sh.chunks, sh.ktiles, sh.ntiles), 256, 0, s>>>(H, ldh, G, ldg, n, K, N,
-                                                                                sh.rows_per_chunk, static_cast<float*>(ws));
+                                                                                sh.rows_per_chunk, partials);
+    gemm_tn_reduce_kernel<<<(K * N + 7) / 8, 256, 0, s>>>(partials, sh.chunks, K, N, out, ldo, beta, 0);
   }
-  gemm_tn_reduce_kernel<<<(K * N + 7) / 8, 256, 0, s>>>(static_cast<const float*>(ws), sh.chunks, K, N, out, ldo, beta);
   return check_launch("cagnet_gemm_tn_f32");
 }
 
