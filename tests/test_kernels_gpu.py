@@ -161,14 +161,14 @@ def test_dropin_spmm_gpu_accumulates_in_place_and_keeps_strides():
 
 
 @pytest.mark.parametrize("n,K,N", [(1000, 602, 16), (777, 16, 41), (300, 41, 16), (513, 128, 64), (129, 7, 3),
-                                   (2000, 64, 130)])
+                                   (2000, 64, 130), (70001, 602, 10), (100, 1000, 16), (50, 1100, 16)])
 @pytest.mark.parametrize("trans", [False, True])
 def test_gemm_nn_and_epilogues(n, K, N, trans):
     g = torch.Generator().manual_seed(n + K)
     X = torch.randn(n, K, generator=g)
     W = torch.randn(N, K, generator=g) if trans else torch.randn(K, N, generator=g)
     Z64 = X.double() @ (W.double().t() if trans else W.double())
-    Xd, Wd = ops.to_padded(X.cuda()), W.cuda()
+    Xd, Wd = _poison_pads(ops.to_padded(X.cuda())), W.cuda()
     _close(ops.gemm_nn(Xd, Wd, trans), Z64)
     _close(ops.gemm_nn(X.cuda(), Wd, trans), Z64)                      # unpadded X (scalar loads)
     _close(ops.gemm_nn(Xd, Wd, trans, ops.EPI_RELU), torch.relu(Z64))
