@@ -42,12 +42,13 @@ def _worker(rank, world, case_path, replication, activations, normalization, ove
     ("train_1d_P1.npz", True, 2, "all_gather"), ("train_1d_P3.npz", True, 0, "broadcast"),
     ("train_1d_P3.npz", False, 2, "broadcast"), ("train_1d_P3.npz", True, 1, "broadcast"),
     ("train_1d_P3.npz", True, 2, "all_gather"), ("train_1d_P3.npz", False, 1, "all_gather"),
-    ("train_1d_P3.npz", True, 5, "all_gather"),
+    ("train_1d_P3.npz", True, 5, "all_gather"), ("train_1d_P3.npz", True, -1, "all_gather"),
+    ("train_15d_P4.npz", True, -1, "all_gather"),
     ("train_1d_P1_plain.npz", True, 2, "all_gather"), ("train_15d_P4.npz", True, 2, "all_gather"),
     ("train_15d_P8.npz", True, 0, "broadcast"), ("train_15d_P8.npz", True, 2, "broadcast")])
 def test_schedule_matches_reference_fixture(golden_dir, name, overlap, groups, collective):
     """broadcast with groups = 0: one broadcast + one multiply per stage (the reference's granularity); 1: all
-    stages in one launch; 2: two launch groups.  all_gather: the 1D blocks travel in one collective per launch
+    stages in one launch; 2: two launch groups; -1: the automatic rule.  all_gather: the 1D blocks travel in one collective per launch
     group (the fixture's last block is shorter than the others, so the padding path is exercised)."""
     path = os.path.join(golden_dir, name)
     d = np.load(path)
