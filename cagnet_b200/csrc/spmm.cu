@@ -9,7 +9,12 @@
 //     gridDim.y tiles, dispatched tile-major so that one column slab of B stays hot in L2;
 //   * rows longer than the plan's threshold (power-law hubs) are taken out of the warp-per-row
 //     pass and processed by a whole 512-thread block each, 16 warps on disjoint nonzero ranges,
-//     combined through shared memory in warp order.
+//     combined through shared memory in warp order;
+//   * blocks with short rows (few nonzeros per row on average) and a narrow B run the lane-group kernel
+//     instead of the warp-per-row one: a warp owns a pool of up to 32 consecutive rows, each of its 32/LPN
+//     lane groups walks one short row at a time and takes the next unclaimed row of the pool when it is
+//     done, so no lane waits for a whole warp's fixed cost per 5-nonzero row; the pool's longer rows are
+//     then multiplied by the whole warp as in the warp-per-row kernel.
 // Every output element is produced by a fixed sequence of operations: results are bit-reproducible
 // run to run, no floating-point atomics anywhere.
 #include <limits.h>
@@ -23,6 +28,9 @@ struct Tuning {
   int spmm_rpb = 4;      // rows (warps) per thread block of the warp-per-row kernel: 1, 2, 4 or 8
   int spmm_long = 2048;         // rows with more nonzeros are listed in the plan (block-per-row kernel)
   int spmm_long_narrow = 2048;  // products narrower than 32 vectors may keep more rows in the warp-per-row pass
+  int spmm_group_max = 64;      // lane-group kernel: rows up to this length are walked by one lane group
+  int spmm_group_avg = 96;      // blocks with at most this many nonzeros per row on average use it (0 = never)
+  int spmm_group_pool = 0;      // rows per warp pool there: 0 = automatic, else 4, 8, 16 or 32
 };
 static Tuning g_tuning;
 
@@ -53,6 +61,39 @@ __device__ __forceinline__ void store_vec(float* p, const float (&x)[VEC]) {
     *reinterpret_cast<float2*>(p) = make_float2(x[0], x[1]);
   } else {
     *p = x[0];
+  }
+}
+
+// Stores the leading `live` (<= VEC) elements of x: the vector that straddles the matrix's last column is written
+// element by element, so that columns [f, ld) of C -- which may belong to the caller -- are never touched.
+template <int VEC>
+__device__ __forceinline__ void store_vec_upto(float* p, const float (&x)[VEC], int live) {
+  if (live >= VEC) {
+    store_vec<VEC>(p, x);
+  } else {
+#pragma unroll
+    for (int j = 0; j < VEC; ++j)
+      if (j < live) p[j] = x[j];
+  }
+}
+
+// C[row, tile columns of this lane] = acc (+ the old value when beta != 0), columns >= f left alone.
+template <int VEC, int LPN, int NV>
+__device__ __forceinline__ void store_row(float* __restrict__ cp, int column0, int f, int nvalid, float beta,
+                                          float (&acc)[NV][VEC]) {
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    if (k < nvalid) {
+      const int live = f - (column0 + k * (LPN * VEC));
+      if (live <= 0) continue;
+      if (beta != 0.f) {
+        float old[VEC];
+        load_vec<VEC>(cp + k * (LPN * VEC), old);      // inside the padded row: reading is harmless
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) acc[k][j] += old[j];
+      }
+      store_vec_upto<VEC>(cp + k * (LPN * VEC), acc[k], live);
+    }
   }
 }
 
@@ -121,10 +162,15 @@ __device__ __forceinline__ void accumulate_range(const int* __restrict__ col, co
         }
       }
     } else {
-      for (int s = 0; s < cnt; s += G) {
-        if (s + sub < cnt) {
-          const int2 q = stage[s + sub];
-          gather(q.x, __int_as_float(q.y));
+      // a short row or the tail of a long one: four predicated steps per trip keep several gathers in flight
+      for (int s = 0; s < cnt; s += 4 * G) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int idx = s + u * G + sub;
+          if (idx < cnt) {
+            const int2 q = stage[idx];
+            gather(q.x, __int_as_float(q.y));
+          }
         }
       }
     }
@@ -152,7 +198,7 @@ constexpr int kMaxRowsPerBlock = 8;
 template <int VEC, int LPN, int NV>
 __global__ void __launch_bounds__(kMaxRowsPerBlock * 32) spmm_warp_rows_kernel(
     const int* __restrict__ rowptr, const int* __restrict__ col, const float* __restrict__ val, int n,
-    const float* __restrict__ B, int ldb, float* __restrict__ C, int ldc, int f_eff, float beta,
+    const float* __restrict__ B, int ldb, float* __restrict__ C, int ldc, int f_eff, int f, float beta,
     const int* __restrict__ plan, int min_threshold) {
   __shared__ __align__(16) int2 stage[kMaxRowsPerBlock][32];
   const int warp = threadIdx.x >> 5;
@@ -175,27 +221,139 @@ __global__ void __launch_bounds__(kMaxRowsPerBlock * 32) spmm_warp_rows_kernel(
 
   accumulate_range<VEC, LPN, NV>(col, val, start, end, B + tile0 + l * VEC, ldb, nvalid, lane, stage[warp], acc);
 
-  if (lane < LPN) {
-    float* cp = C + static_cast<int64_t>(row) * ldc + tile0 + l * VEC;
+  if (lane < LPN)
+    store_row<VEC, LPN, NV>(C + static_cast<int64_t>(row) * ldc + tile0 + l * VEC, tile0 + l * VEC, f, nvalid, beta, acc);
+}
+
+// ------------------------------------------------------------------------------------------------
+// Lane-group kernel for blocks of short rows (LPN < 32).
+//
+// A warp owns a pool of `pool` (<= 32) consecutive rows; lane i keeps row i's [start, end).  Rows are sorted
+// into three classes by length alone, so the arithmetic of a row never depends on scheduling:
+//   short   (<= group_max nonzeros): walked by ONE lane group (LPN lanes, each VEC*NV output columns), nonzero
+//           after nonzero in order, UNROLL gathers in flight per group; a group that finishes takes the next
+//           unclaimed short row of the pool (ballot + bit tricks, no memory traffic), so the 32/LPN groups stay
+//           busy although their rows differ in length;
+//   medium  (<= the plan's hub threshold): multiplied by the whole warp exactly as in the warp-per-row kernel
+//           (pairs staged through shared memory, lane groups on interleaved nonzeros, shuffle fold);
+//   hub     rows are skipped: the block-per-row kernel owns them.
+// Per short row this costs a few instructions of bookkeeping instead of a warp's offsets load, stage, two
+// warp barriers and a shuffle tree.
+template <int VEC, int LPN, int NV>
+__global__ void __launch_bounds__(kMaxRowsPerBlock * 32) spmm_group_rows_kernel(
+    const int* __restrict__ rowptr, const int* __restrict__ col, const float* __restrict__ val, int n,
+    const float* __restrict__ B, int ldb, float* __restrict__ C, int ldc, int f_eff, int f, float beta,
+    const int* __restrict__ plan, int min_threshold, int group_max, int pool) {
+  static_assert(LPN < 32, "the lane-group kernel needs at least two groups per warp");
+  constexpr int G = 32 / LPN;
+  constexpr int UNROLL = (NV >= 2) ? 4 : 8;
+  __shared__ __align__(16) int2 stage[kMaxRowsPerBlock][32];
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int row0 = (blockIdx.x * (blockDim.x >> 5) + warp) * pool;
+  if (row0 >= n) return;                      // whole warps leave together; nothing below is block-wide
+  const int l = lane % LPN;
+  const int sub = lane / LPN;
+  const int tile0 = blockIdx.y * (LPN * VEC * NV);
+  const int column0 = tile0 + l * VEC;
+  const int nvalid = live_vectors<VEC, LPN, NV>(tile0, l, f_eff);
+  const float* bt = B + column0;
+  const int long_threshold = plan ? max(__ldg(plan + 2), min_threshold) : INT_MAX;
+
+  // lane i: offsets of row row0 + i
+  const bool have = lane < pool && row0 + lane < n;
+  const int my_start = have ? __ldg(rowptr + row0 + lane) : 0;
+  const int my_end = have ? __ldg(rowptr + row0 + lane + 1) : 0;
+  const int my_len = my_end - my_start;
+  unsigned pending = __ballot_sync(0xffffffffu, have && my_len <= group_max);
+  unsigned medium = __ballot_sync(0xffffffffu, have && my_len > group_max && my_len <= long_threshold);
+
+  float acc[NV][VEC];
+  int cur = -1, e = 0, e_end = 0;             // the group's row (pool index) and its nonzero cursor
+  for (;;) {
+    const bool need = e >= e_end;             // uniform inside a lane group
+    if (need && cur >= 0) {
+      // every lane of the group holds its own columns of the row
+      store_row<VEC, LPN, NV>(C + static_cast<int64_t>(row0 + cur) * ldc + column0, column0, f, nvalid, beta, acc);
+      cur = -1;
+    }
+    // groups without a row claim the pool's next short rows, lowest group first
+    const unsigned need_lanes = __ballot_sync(0xffffffffu, need);
+    if (need_lanes) {
+      unsigned groups = 0;                    // bit g: lane group g wants a row
 #pragma unroll
-    for (int k = 0; k < NV; ++k) {
-      if (k < nvalid) {
-        if (beta != 0.f) {
-          float old[VEC];
-          load_vec<VEC>(cp + k * (LPN * VEC), old);
+      for (int g = 0; g < G; ++g) groups |= ((need_lanes >> (g * LPN)) & 1u) << g;
+      const int rank = __popc(groups & ((1u << sub) - 1u));
+      unsigned mine = pending;
+      for (int i = 0; i < rank; ++i) mine &= mine - 1;            // drop the rows taken by lower groups
+      const int pick = (need && mine) ? __ffs(mine) - 1 : -1;
+      for (int i = __popc(groups); i > 0 && pending; --i) pending &= pending - 1;
+      const int src = pick < 0 ? 0 : pick;
+      const int s_new = __shfl_sync(0xffffffffu, my_start, src);
+      const int e_new = __shfl_sync(0xffffffffu, my_end, src);
+      if (need) {
+        cur = pick;
+        e = pick < 0 ? 0 : s_new;
+        e_end = pick < 0 ? 0 : e_new;
 #pragma unroll
-          for (int j = 0; j < VEC; ++j) acc[k][j] += old[j];
+        for (int k = 0; k < NV; ++k)
+#pragma unroll
+          for (int j = 0; j < VEC; ++j) acc[k][j] = 0.f;
+      }
+      if (__ballot_sync(0xffffffffu, cur >= 0) == 0) break;      // pool exhausted and every group is done
+    }
+    // up to UNROLL nonzeros of the group's row: offsets first, then the gathers, then the FMAs in order
+    int c[UNROLL];
+    float v[UNROLL];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const bool ok = e + u < e_end;
+      c[u] = ok ? __ldg(col + e + u) : -1;
+      v[u] = ok ? __ldg(val + e + u) : 0.f;
+    }
+    float x[UNROLL][NV][VEC];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const float* bp = bt + static_cast<int64_t>(c[u] < 0 ? 0 : c[u]) * ldb;
+#pragma unroll
+      for (int k = 0; k < NV; ++k) {
+        if (c[u] >= 0 && k < nvalid) {
+          load_vec<VEC>(bp + k * (LPN * VEC), x[u][k]);
+        } else {
+#pragma unroll
+          for (int j = 0; j < VEC; ++j) x[u][k][j] = 0.f;
         }
-        store_vec<VEC>(cp + k * (LPN * VEC), acc[k]);
       }
     }
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u)
+#pragma unroll
+      for (int k = 0; k < NV; ++k)
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) acc[k][j] = fmaf(v[u], x[u][k][j], acc[k][j]);
+    e = min(e + UNROLL, e_end);
+  }
+
+  // the pool's medium rows, one after the other, by the whole warp
+  while (medium) {
+    const int i = __ffs(medium) - 1;
+    medium &= medium - 1;
+    const int start = __shfl_sync(0xffffffffu, my_start, i);
+    const int end = __shfl_sync(0xffffffffu, my_end, i);
+#pragma unroll
+    for (int k = 0; k < NV; ++k)
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) acc[k][j] = 0.f;
+    accumulate_range<VEC, LPN, NV>(col, val, start, end, bt, ldb, nvalid, lane, stage[warp], acc);
+    if (lane < LPN)
+      store_row<VEC, LPN, NV>(C + static_cast<int64_t>(row0 + i) * ldc + column0, column0, f, nvalid, beta, acc);
   }
 }
 
 template <int VEC, int LPN, int NV>
 __global__ void __launch_bounds__(kLongWarps * 32) spmm_block_rows_kernel(
     const int* __restrict__ rowptr, const int* __restrict__ col, const float* __restrict__ val,
-    const float* __restrict__ B, int ldb, float* __restrict__ C, int ldc, int f_eff, float beta,
+    const float* __restrict__ B, int ldb, float* __restrict__ C, int ldc, int f_eff, int f, float beta,
     const int* __restrict__ plan, int min_threshold) {
   constexpr int TILE = LPN * VEC * NV;
   __shared__ float part[kLongWarps][TILE];
@@ -234,7 +392,7 @@ __global__ void __launch_bounds__(kLongWarps * 32) spmm_block_rows_kernel(
     __syncthreads();
     for (int idx = threadIdx.x; idx < TILE; idx += blockDim.x) {
       const int column = tile0 + idx;
-      if (column < f_eff) {
+      if (column < f) {
         float s = part[0][idx];
 #pragma unroll
         for (int w = 1; w < kLongWarps; ++w) s += part[w][idx];
@@ -280,9 +438,18 @@ __global__ void spmm_plan_header_kernel(int threshold, int capacity, int* plan) 
 
 static int plan_capacity(int64_t nnz, int threshold) { return static_cast<int>(nnz / threshold) + 1; }
 
+// Rows per pool of the lane-group kernel: 32 when that still leaves every SM a few dozen warps, fewer for small blocks.
+static int group_pool_rows(int n) {
+  if (g_tuning.spmm_group_pool > 0) return g_tuning.spmm_group_pool;
+  const int want_warps = kNumSMs * 32;
+  int pool = 32;
+  while (pool > 4 && (n + pool - 1) / pool < want_warps) pool >>= 1;
+  return pool;
+}
+
 template <int VEC, int LPN, int NV>
 static int launch_spmm(const int* rowptr, const int* col, const float* val, int n, int m, int64_t nnz, const float* B,
-                       int64_t ldb64, float* C, int64_t ldc64, int f_eff, float beta, const int* plan,
+                       int64_t ldb64, float* C, int64_t ldc64, int f_eff, int f, float beta, const int* plan,
                        cudaStream_t stream) {
   const int ldb = static_cast<int>(ldb64), ldc = static_cast<int>(ldc64);   // checked to fit by the entry point
   (void)m;
@@ -294,11 +461,21 @@ static int launch_spmm(const int* rowptr, const int* col, const float* val, int 
     // current threshold and never below one wave
     const int blocks = max(1, min(plan_capacity(nnz, max(g_tuning.spmm_long, kMinLongThreshold)), 16 * kNumSMs));
     spmm_block_rows_kernel<VEC, LPN, NV><<<dim3(blocks, tiles), kLongWarps * 32, 0, stream>>>(
-        rowptr, col, val, B, ldb, C, ldc, f_eff, beta, plan, min_threshold);
+        rowptr, col, val, B, ldb, C, ldc, f_eff, f, beta, plan, min_threshold);
   }
   const int rows_per_block = g_tuning.spmm_rpb;
+  if constexpr (LPN < 32) {
+    if (g_tuning.spmm_group_avg > 0 && nnz <= static_cast<int64_t>(g_tuning.spmm_group_avg) * n) {
+      const int pool = group_pool_rows(n);
+      const int pools = (n + pool - 1) / pool;
+      spmm_group_rows_kernel<VEC, LPN, NV><<<dim3((pools + rows_per_block - 1) / rows_per_block, tiles),
+                                             rows_per_block * 32, 0, stream>>>(
+          rowptr, col, val, n, B, ldb, C, ldc, f_eff, f, beta, plan, min_threshold, g_tuning.spmm_group_max, pool);
+      return check_launch("cagnet_spmm_csr_f32");
+    }
+  }
   spmm_warp_rows_kernel<VEC, LPN, NV><<<dim3((n + rows_per_block - 1) / rows_per_block, tiles), rows_per_block * 32, 0,
-                                        stream>>>(rowptr, col, val, n, B, ldb, C, ldc, f_eff, beta, plan, min_threshold);
+                                        stream>>>(rowptr, col, val, n, B, ldb, C, ldc, f_eff, f, beta, plan, min_threshold);
   return check_launch("cagnet_spmm_csr_f32");
 }
 
@@ -316,10 +493,10 @@ static int auto_tile(int vectors) {
 
 template <int VEC>
 static int dispatch_shape(int vectors, const int* rowptr, const int* col, const float* val, int n, int m, int64_t nnz,
-                          const float* B, int64_t ldb, float* C, int64_t ldc, int f_eff, float beta, const int* plan,
-                          cudaStream_t stream) {
+                          const float* B, int64_t ldb, float* C, int64_t ldc, int f_eff, int f, float beta,
+                          const int* plan, cudaStream_t stream) {
 #define CAGNET_SPMM_CASE(LPN, NV) \
-  return launch_spmm<VEC, LPN, NV>(rowptr, col, val, n, m, nnz, B, ldb, C, ldc, f_eff, beta, plan, stream)
+  return launch_spmm<VEC, LPN, NV>(rowptr, col, val, n, m, nnz, B, ldb, C, ldc, f_eff, f, beta, plan, stream)
   int tile = g_tuning.spmm_tile > 0 ? g_tuning.spmm_tile : auto_tile(vectors);
   if (vectors <= 4) tile = 4;
   if (g_tuning.spmm_tile == 0 && vectors > 4 && vectors <= 16) {
@@ -372,6 +549,22 @@ extern "C" int cagnet_set_param(const char* name, int value) {
     g_tuning.spmm_long_narrow = value;
     return CAGNET_OK;
   }
+  if (!strcmp(name, "spmm_group_max")) {
+    if (value < 0 || value > 4096) return fail(CAGNET_E_ARG, "cagnet_set_param: spmm_group_max must be in [0, 4096]");
+    g_tuning.spmm_group_max = value;
+    return CAGNET_OK;
+  }
+  if (!strcmp(name, "spmm_group_pool")) {
+    if (value != 0 && value != 4 && value != 8 && value != 16 && value != 32)
+      return fail(CAGNET_E_ARG, "cagnet_set_param: spmm_group_pool must be 0, 4, 8, 16 or 32");
+    g_tuning.spmm_group_pool = value;
+    return CAGNET_OK;
+  }
+  if (!strcmp(name, "spmm_group_avg")) {
+    if (value < 0) return fail(CAGNET_E_ARG, "cagnet_set_param: spmm_group_avg must be >= 0");
+    g_tuning.spmm_group_avg = value;
+    return CAGNET_OK;
+  }
   if (!strcmp(name, "spmm_long")) {
     if (value < kMinLongThreshold) return fail(CAGNET_E_ARG, "cagnet_set_param: spmm_long must be >= 256");
     g_tuning.spmm_long = value;
@@ -385,6 +578,9 @@ extern "C" int cagnet_get_param(const char* name) {
   if (name && !strcmp(name, "spmm_rpb")) return g_tuning.spmm_rpb;
   if (name && !strcmp(name, "spmm_long")) return g_tuning.spmm_long;
   if (name && !strcmp(name, "spmm_long_narrow")) return g_tuning.spmm_long_narrow;
+  if (name && !strcmp(name, "spmm_group_max")) return g_tuning.spmm_group_max;
+  if (name && !strcmp(name, "spmm_group_avg")) return g_tuning.spmm_group_avg;
+  if (name && !strcmp(name, "spmm_group_pool")) return g_tuning.spmm_group_pool;
   if (name && !strcmp(name, "core_chunk")) return core_chunk();
   return -1;
 }
@@ -411,32 +607,42 @@ extern "C" int cagnet_spmm_plan_i32(const int32_t* rowptr, int32_t n, int64_t nn
   return check_launch("cagnet_spmm_plan_i32");
 }
 
+// Argument checks shared by the two multiply entry points; `who` names the caller in the error text.
+static int check_spmm_args(const char* who, const int32_t* rowptr, const int32_t* col, const float* val, int32_t n,
+                           int32_t m, int64_t nnz, const float* B, int64_t ldb, float* C, int64_t ldc, int32_t f,
+                           float beta) {
+  if (n < 0 || m < 0 || nnz < 0 || f < 0) return fail(CAGNET_E_ARG, "%s: negative size", who);
+  if (n == 0 || f == 0) return CAGNET_OK;
+  if (!rowptr || !C || (nnz > 0 && (!col || !val || !B))) return fail(CAGNET_E_ARG, "%s: null pointer", who);
+  if (beta != 0.f && beta != 1.f) return fail(CAGNET_E_ARG, "%s: beta must be 0 or 1", who);
+  if (nnz > INT_MAX) return fail(CAGNET_E_OVERFLOW, "%s: nnz %lld exceeds int32", who, nnz);
+  if (ldb < f || ldc < f)
+    return fail(CAGNET_E_ALIGN, "%s: leading dimension (%lld, %lld) smaller than f", who, ldb, ldc);
+  if (ldb > INT_MAX || ldc > INT_MAX)
+    return fail(CAGNET_E_OVERFLOW, "%s: leading dimension (%lld, %lld) exceeds int32", who, ldb, ldc);
+  return CAGNET_OK;
+}
+
 extern "C" int cagnet_spmm_csr_f32(const int32_t* rowptr, const int32_t* col, const float* val, int32_t n, int32_t m,
                                    int64_t nnz, const float* B, int64_t ldb, float* C, int64_t ldc, int32_t f,
                                    float beta, const void* plan, void* stream) {
-  if (n < 0 || m < 0 || nnz < 0 || f < 0) return fail(CAGNET_E_ARG, "cagnet_spmm_csr_f32: negative size");
-  if (n == 0 || f == 0) return CAGNET_OK;
-  if (!rowptr || !C || (nnz > 0 && (!col || !val || !B)))
-    return fail(CAGNET_E_ARG, "cagnet_spmm_csr_f32: null pointer");
-  if (beta != 0.f && beta != 1.f) return fail(CAGNET_E_ARG, "cagnet_spmm_csr_f32: beta must be 0 or 1");
-  if (nnz > INT_MAX) return fail(CAGNET_E_OVERFLOW, "cagnet_spmm_csr_f32: nnz %s%lld exceeds int32", "", nnz);
-  if (ldb < f || ldc < f)
-    return fail(CAGNET_E_ALIGN, "cagnet_spmm_csr_f32: leading dimension%s (%lld, %lld) smaller than f", "", ldb, ldc);
-  if (ldb > INT_MAX || ldc > INT_MAX)
-    return fail(CAGNET_E_OVERFLOW, "cagnet_spmm_csr_f32: leading dimension%s (%lld, %lld) exceeds int32", "", ldb, ldc);
+  const int rc = check_spmm_args("cagnet_spmm_csr_f32", rowptr, col, val, n, m, nnz, B, ldb, C, ldc, f, beta);
+  if (rc != CAGNET_OK || n == 0 || f == 0) return rc;
   if (!B) B = C;  // nnz == 0: never dereferenced
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int* p = static_cast<const int*>(plan);
   auto round_up = [](int x, int a) { return (x + a - 1) / a * a; };
+  // Vector width by alignment.  Columns [f, round_up(f)) of B's padded rows are read (and their products thrown
+  // away); C is only ever written below column f.
   if (ldb % 4 == 0 && ldc % 4 == 0 && aligned(B, 16) && aligned(C, 16) && round_up(f, 4) <= ldb && round_up(f, 4) <= ldc) {
     const int f_eff = round_up(f, 4);
-    return dispatch_shape<4>(f_eff / 4, rowptr, col, val, n, m, nnz, B, ldb, C, ldc, f_eff, beta, p, s);
+    return dispatch_shape<4>(f_eff / 4, rowptr, col, val, n, m, nnz, B, ldb, C, ldc, f_eff, f, beta, p, s);
   }
   if (ldb % 2 == 0 && ldc % 2 == 0 && aligned(B, 8) && aligned(C, 8) && round_up(f, 2) <= ldb && round_up(f, 2) <= ldc) {
     const int f_eff = round_up(f, 2);
-    return dispatch_shape<2>(f_eff / 2, rowptr, col, val, n, m, nnz, B, ldb, C, ldc, f_eff, beta, p, s);
+    return dispatch_shape<2>(f_eff / 2, rowptr, col, val, n, m, nnz, B, ldb, C, ldc, f_eff, f, beta, p, s);
   }
-  return dispatch_shape<1>(f, rowptr, col, val, n, m, nnz, B, ldb, C, ldc, f, beta, p, s);
+  return dispatch_shape<1>(f, rowptr, col, val, n, m, nnz, B, ldb, C, ldc, f, f, beta, p, s);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -464,7 +670,8 @@ static int static_plan_address(int** out) {
   if (e != cudaSuccess || device < 0 || device >= kMaxDevices)
     return fail(CAGNET_E_LAUNCH, "cagnet_spmm_csr_f32_noalloc: cannot identify the current device%s (%lld)", "",
                 static_cast<long long>(device));
-  if (!g_static_plan_addr[device]) {
+  // concurrent first calls on one device all obtain the same address; the slot is read and written atomically
+  if (!__atomic_load_n(&g_static_plan_addr[device], __ATOMIC_ACQUIRE)) {
     int* p = nullptr;
     e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_static_plan);
     if (e != cudaSuccess || !p) {
@@ -472,9 +679,9 @@ static int static_plan_address(int** out) {
                cudaGetErrorString(e));
       return CAGNET_E_LAUNCH;
     }
-    g_static_plan_addr[device] = p;
+    __atomic_store_n(&g_static_plan_addr[device], p, __ATOMIC_RELEASE);
   }
-  *out = g_static_plan_addr[device];
+  *out = __atomic_load_n(&g_static_plan_addr[device], __ATOMIC_ACQUIRE);
   return CAGNET_OK;
 }
 
@@ -488,10 +695,9 @@ extern "C" int64_t cagnet_spmm_noalloc_max_nnz(void) {
 extern "C" int cagnet_spmm_csr_f32_noalloc(const int32_t* rowptr, const int32_t* col, const float* val, int32_t n,
                                            int32_t m, int64_t nnz, const float* B, int64_t ldb, float* C, int64_t ldc,
                                            int32_t f, float beta, void* stream) {
-  if (n < 0 || m < 0 || nnz < 0 || f < 0) return fail(CAGNET_E_ARG, "cagnet_spmm_csr_f32_noalloc: negative size");
-  if (n == 0 || f == 0) return CAGNET_OK;
-  if (!rowptr) return fail(CAGNET_E_ARG, "cagnet_spmm_csr_f32_noalloc: null pointer");
-  if (nnz > INT_MAX) return fail(CAGNET_E_OVERFLOW, "cagnet_spmm_csr_f32_noalloc: nnz %s%lld exceeds int32", "", nnz);
+  // every argument is checked before anything is queued: a rejected call leaves the shared list as it was
+  const int arc = check_spmm_args("cagnet_spmm_csr_f32_noalloc", rowptr, col, val, n, m, nnz, B, ldb, C, ldc, f, beta);
+  if (arc != CAGNET_OK || n == 0 || f == 0) return arc;
   if (nnz > cagnet_spmm_noalloc_max_nnz())
     return fail(CAGNET_E_WORKSPACE,
                 "cagnet_spmm_csr_f32_noalloc: %s%lld nonzeros exceed the built-in scratch (at most %lld at the current "

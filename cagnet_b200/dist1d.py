@@ -18,7 +18,7 @@ import torch.nn.functional as F
 
 from . import partition
 from .backend import ACT_LOG_SOFTMAX, ACT_NONE, ACT_RELU
-from .timing import CATEGORIES_15D, CATEGORIES_1D, Timers
+from .timing import CATEGORIES_15D, CATEGORIES_1D, Timers, all_gather_bytes, all_reduce_bytes
 
 
 class Data:
@@ -38,7 +38,7 @@ class Runtime:
     """Per-process settings: what the reference keeps in module globals (gcn_distr.py:53-64)."""
 
     def __init__(self, backend, activations=True, normalization=True, replication=1, timing=False, overlap=True,
-                 categories=None, order="reference", stage_groups=-1, collective="all_gather"):
+                 categories=None, order="reference", stage_groups=-1, collective="all_gather", prefetch_features=False):
         if order not in ("reference", "min_width"):
             raise ValueError("order must be 'reference' or 'min_width'")
         if collective not in ("all_gather", "broadcast"):
@@ -54,6 +54,16 @@ class Runtime:
         self.normalization = bool(normalization)
         self.replication = int(replication)
         self.overlap = bool(overlap)
+        # 1D all-gather schedule only: the vertex features never change between epochs (the reference reads the same
+        # `inputs_loc` every epoch, gcn_distr.py:595-601), so the all-gather of layer 1 for epoch k+1 depends on
+        # nothing epoch k computes.  With this on it is issued, on a communicator of its own, as soon as epoch k's
+        # layer-1 multiply is queued and travels under the rest of epoch k; the same bytes move every epoch.
+        # `next_features` = (tensor, event or None): the features of the NEXT epoch when they differ from the current
+        # ones (a loader that refills a second buffer) and the event that marks them ready.
+        self.prefetch_features = bool(prefetch_features)
+        self.prefetch_group = None
+        self.next_features = None
+        self.layer1_input = None
         cats = categories or (CATEGORIES_15D if replication > 1 else CATEGORIES_1D)
         self.timers = Timers(cats, timing, getattr(backend, "synchronize", None))
 
@@ -82,10 +92,10 @@ class StagePlan:
     Fewer groups trade pipeline depth for larger multiplies: on a 233K-vertex graph split 8 ways one launch per
     stage spends most of its time on per-launch and per-row-segment overheads (6.5 ms against 4.1 ms for the same
     nonzeros in one launch at width 602, 1.29 ms against 0.39 ms at width 16), while the broadcasts it could hide
-    take 0.7 ms in total.  The default of two groups keeps the broadcast of the second half behind the multiply of
-    the first."""
+    take 0.7 ms in total.  `Model` passes one group unless told otherwise; two keep the broadcast of the second half
+    behind the multiply of the first."""
 
-    def __init__(self, backend, blocks, rank, size, replication, groups=2):
+    def __init__(self, backend, blocks, rank, size, replication, groups=1):
         stages = partition.stages_15d(rank, size, replication)
         self.n_loc = blocks[0].n_rows
         n_groups = max(1, min(len(stages), groups if groups and groups > 0 else len(stages)))
@@ -114,9 +124,12 @@ class GatherPlan:
     One NCCL call moves what P broadcast calls moved; at 8 GPUs and width 602 the eight 70 MB broadcasts cost
     about 2.5 ms per product, the all-gather of the same bytes well under 1 ms."""
 
-    def __init__(self, backend, blocks, rank, size, n_per_proc, groups=2):
+    def __init__(self, backend, blocks, rank, size, n_per_proc, groups=1):
         self.n_loc = blocks[0].n_rows
         self.size = size
+        # feature prefetch (Runtime.prefetch_features): {(data pointer, width): [(buffer, work)]} posted for the next
+        # epoch, two buffer sets used in turn
+        self.prefetched, self.prefetch_bufs, self.flip = {}, {}, 0
         n_groups = max(1, min(groups if groups and groups > 0 else 1, n_per_proc))
         bounds = [round(g * n_per_proc / n_groups) for g in range(n_groups + 1)]
         self.groups = []
@@ -140,30 +153,41 @@ def _gather_func(rt, plan, inputs, rank, size, group):
     comm = size > 1 and dist.is_initialized()
     z = be.empty(plan.n_loc, f)
     bufs = [None, None]
+    ld = inputs.stride(0) if inputs.size(0) > 1 else f                  # floats per row on the wire
+
+    def send_rows(src, g):
+        have = max(0, min(src.size(0), g.lo + g.rows) - g.lo)          # the last block may end inside the range
+        if have == g.rows:
+            return src[g.lo:g.lo + g.rows]
+        send = be.zeros(g.rows, f)
+        if have > 0:
+            be.wire(send[:have]).copy_(be.wire(src[g.lo:g.lo + have]))
+        return send
 
     def post(gi):
         g = plan.groups[gi]
-        have = max(0, min(inputs.size(0), g.lo + g.rows) - g.lo)      # the last block may end inside the range
-        if have == g.rows:
-            send = inputs[g.lo:g.lo + g.rows]
-        else:
-            send = be.zeros(g.rows, f)
-            if have > 0:
-                be.wire(send[:have]).copy_(be.wire(inputs[g.lo:g.lo + have]))
+        send = send_rows(inputs, g)
         if not comm:
             return send, None
         if bufs[gi % 2] is None:
             bufs[gi % 2] = be.empty(size * max(gg.rows for gg in plan.groups), f)
         recv = bufs[gi % 2][:size * g.rows]
         rt.timers.count("bcast_words", size * g.rows * f)
+        rt.timers.traffic("h_all_gather", all_gather_bytes(g.rows * ld * 4, size))
         work = dist.all_gather_into_tensor(be.wire(recv), be.wire(send), group=group, async_op=True)
         return recv, work
 
     serial = rt.timers.enabled or not rt.overlap
+    layer1 = comm and rt.prefetch_features and rt.layer1_input is not None and inputs.data_ptr() == rt.layer1_input
+    ready = plan.prefetched.pop((inputs.data_ptr(), f), None) if layer1 else None
     pending = None
     for gi, g in enumerate(plan.groups):
-        if serial:
-            with rt.timers.region("comm_time", "bcast_comm_time"):
+        if ready is not None:
+            tensor, work = ready[gi]
+            if work is not None:
+                work.wait()
+        elif serial:
+            with rt.timers.region("comm_time", "bcast_comm_time", "link:h_all_gather"):
                 tensor, work = post(gi)
                 if work is not None:
                     work.wait()
@@ -174,6 +198,24 @@ def _gather_func(rt, plan, inputs, rank, size, group):
                 work.wait()
         with rt.timers.region("comp_time", "scomp_time"):
             be.spmm(g.block, tensor, z, 0.0 if gi == 0 else 1.0)
+    if layer1 and not rt.timers.enabled:
+        # next epoch's gather of the features, into the buffer set this epoch did not read
+        nxt, event = rt.next_features if rt.next_features is not None else (inputs, None)
+        nxt = be.as_matrix(nxt)
+        if event is not None:
+            torch.cuda.current_stream().wait_event(event)
+        plan.flip ^= 1
+        posted = []
+        for gi, g in enumerate(plan.groups):
+            key = (plan.flip, gi)
+            if key not in plan.prefetch_bufs:
+                plan.prefetch_bufs[key] = be.empty(size * g.rows, f)
+            recv = plan.prefetch_bufs[key]
+            rt.timers.count("bcast_words", size * g.rows * f)
+            rt.timers.traffic("h_all_gather", all_gather_bytes(g.rows * ld * 4, size))
+            posted.append((recv, dist.all_gather_into_tensor(be.wire(recv), be.wire(send_rows(nxt, g)),
+                                                             group=rt.prefetch_group, async_op=True)))
+        plan.prefetched = {(nxt.data_ptr(), f): posted}
     return z
 
 
@@ -223,6 +265,7 @@ def _broadcast_func(rt, node_count, am_partitions, inputs, rank, size, row_group
         for piece, q in pieces:
             rt.timers.count("bcast_words", piece.size(0) * f)
             if comm:
+                rt.timers.traffic("h_broadcast", be.wire(piece).numel() * 4)
                 works.append(dist.broadcast(be.wire(piece), src=q, group=col_group, async_op=True))
         return tensor, works
 
@@ -230,7 +273,7 @@ def _broadcast_func(rt, node_count, am_partitions, inputs, rank, size, row_group
     pending = None
     for gi, g in enumerate(plan.groups):
         if serial:
-            with rt.timers.region("comm_time", "bcast_comm_time"):
+            with rt.timers.region("comm_time", "bcast_comm_time", "link:h_broadcast"):
                 tensor, works = post(gi)
                 for w in works:
                     w.wait()
@@ -242,7 +285,8 @@ def _broadcast_func(rt, node_count, am_partitions, inputs, rank, size, row_group
         with rt.timers.region("comp_time", "scomp_time"):
             be.spmm(g.block, tensor, z, 0.0 if gi == 0 else 1.0)
     if c > 1 and comm:
-        with rt.timers.region("comm_time", "reduce_comm_time"):
+        with rt.timers.comm("z_replica_all_reduce", all_reduce_bytes(be.wire(z).numel() * 4, c), "comm_time",
+                            "reduce_comm_time"):
             dist.all_reduce(be.wire(z), op=dist.ReduceOp.SUM, group=row_group)
     return z
 
@@ -253,7 +297,9 @@ def outer_product2(rt, inputs, ag, rank, size, group):
     with rt.timers.region("comp_time", "dcomp_time"):
         grad_weight = be.mm_tn(be.as_matrix(inputs), ag)
     if size > 1 and dist.is_initialized():
-        with rt.timers.region("comm_time", "op2_comm_time", "op_comm_time"):
+        members = size // rt.replication
+        with rt.timers.comm("grad_w_all_reduce", all_reduce_bytes(grad_weight.numel() * 4, members), "comm_time",
+                            "op2_comm_time", "op_comm_time"):
             dist.all_reduce(grad_weight, op=dist.ReduceOp.SUM, group=group)
     return grad_weight
 
@@ -357,6 +403,9 @@ class Model:
         groups = rt.stage_groups if rt.stage_groups >= 0 else 1
         if c == 1 and size > 1 and rt.collective == "all_gather":
             self.am_pbyp = GatherPlan(be, blocks, rank, size, n_per_proc, groups)
+            if rt.prefetch_features and dist.is_initialized() and rt.prefetch_group is None:
+                # a communicator of its own: the prefetch must not queue in front of the epoch's other collectives
+                rt.prefetch_group = dist.new_group(list(range(size)))
         else:
             self.am_pbyp = StagePlan(be, blocks, rank, size, c, groups)
         rank_c = rank // c
@@ -416,8 +465,10 @@ def train(inputs, weight1, weight2, adj_matrix, am_partitions, optimizer, model,
           col_groups, rt):
     """One epoch: two layers, the rank-local mean NLL over its own train rows, backward, Adam step.
     gcn_distr.py:341-366.  `model` supplies this rank's label / mask slices and its train-row count."""
+    rt.layer1_input = inputs.data_ptr()       # what the feature prefetch recognises the first layer's multiply by
     outputs = GCNFunc.apply(inputs, weight1, adj_matrix, am_partitions, rank, size, group, row_groups, col_groups,
                             F.relu, rt)
+    rt.layer1_input = None
     outputs = GCNFunc.apply(outputs, weight2, adj_matrix, am_partitions, rank, size, group, row_groups, col_groups,
                             F.log_softmax, rt)
     optimizer.zero_grad()

@@ -24,7 +24,7 @@ import torch.nn.functional as F
 from . import partition
 from .backend import ACT_LOG_SOFTMAX, ACT_NONE, ACT_RELU
 from .dist1d import Data, act_name  # noqa: F401  (Data re-exported for callers of this module)
-from .timing import CATEGORIES_2D, Timers
+from .timing import CATEGORIES_2D, Timers, all_gather_bytes, all_reduce_bytes
 
 
 class Runtime:
@@ -94,7 +94,7 @@ def summa_sparse(model, inputs):
         if src == g.rank:
             blk = model.adj_block
             if g.comm and not (rt.cache_blocks and model.blocks_sent):
-                with rt.timers.region("comm_time", "summa_sparse_bcast1"):
+                with rt.timers.comm("a_block_broadcast", model.adj_wire.numel() * 4, "comm_time", "summa_sparse_bcast1"):
                     _bcast(model.adj_wire, src, g.row_group)
                 rt.timers.count("summa_sparse_bcast1_words", model.adj_wire.numel())
             return blk
@@ -102,7 +102,7 @@ def summa_sparse(model, inputs):
             return model.block_cache[k]
         n_r, n_c, nnz = model.row_sizes[g.row], model.row_sizes[k], model.nnz_of[src]
         buf = be.wire_buffer(n_r, nnz)
-        with rt.timers.region("comm_time", "summa_sparse_bcast1"):
+        with rt.timers.comm("a_block_broadcast", buf.numel() * 4, "comm_time", "summa_sparse_bcast1"):
             _bcast(buf, src, g.row_group)
         rt.timers.count("summa_sparse_bcast1_words", buf.numel())
         blk = be.block_from_wire(buf, n_r, n_c, nnz, reused=rt.cache_blocks)
@@ -120,6 +120,8 @@ def summa_sparse(model, inputs):
                 bufs[k % 2] = be.empty(max(model.row_sizes), f_col)
             tensor = bufs[k % 2][:rows]
         rt.timers.count("summa_sparse_bcast2_words", rows * f_col)
+        if g.comm:
+            rt.timers.traffic("h_broadcast", be.wire(tensor).numel() * 4)
         work = _bcast(be.wire(tensor), src, g.col_group, async_op=True) if g.comm else None
         return tensor, work
 
@@ -128,7 +130,7 @@ def summa_sparse(model, inputs):
     for k in range(q):
         blk = a_block(k)
         if serial:
-            with rt.timers.region("comm_time", "summa_sparse_bcast2"):
+            with rt.timers.region("comm_time", "summa_sparse_bcast2", "link:h_broadcast"):
                 tensor, work = post_h(k)
                 if work is not None:
                     work.wait()
@@ -163,7 +165,7 @@ def summa_loc(model, mata, weight, transposed):
         else:
             acol = be.empty(n_r, k_sizes[k])
         if g.comm:
-            with rt.timers.region("comm_time", "summa_loc_bcast"):
+            with rt.timers.comm("z_block_broadcast", be.wire(acol).numel() * 4, "comm_time", "summa_loc_bcast"):
                 _bcast(be.wire(acol), src, g.row_group)
         if transposed:
             part = w[oo[g.col]:oo[g.col + 1], ko[k]:ko[k + 1]]       # used transposed: (out chunk) x (k chunk)
@@ -187,8 +189,9 @@ def transpose(model, mat, total_width):
     f_sizes = partition.chunk_sizes(total_width, g.q)
     recv = be.empty(model.row_sizes[g.col], f_sizes[g.row])
     ops = [dist.P2POp(dist.isend, be.wire(mat), g.rank_t), dist.P2POp(dist.irecv, be.wire(recv), g.rank_t)]
-    for work in dist.batch_isend_irecv(ops):
-        work.wait()
+    with model.rt.timers.comm("transpose_exchange", be.wire(recv).numel() * 4):
+        for work in dist.batch_isend_irecv(ops):
+            work.wait()
     return recv
 
 
@@ -206,9 +209,9 @@ def summa_tn(model, ht, ag, f_in, f_out):
         acol = ht if row_src == g.rank else be.empty(n_k, f_sizes[g.row])
         brow = ag if col_src == g.rank else be.empty(n_k, o_sizes[g.col])
         if g.comm:
-            with rt.timers.region("comm_time", "summa_bcast1"):
+            with rt.timers.comm("grad_w_summa_broadcast", be.wire(acol).numel() * 4, "comm_time", "summa_bcast1"):
                 _bcast(be.wire(acol), row_src, g.row_group)
-            with rt.timers.region("comm_time", "summa_bcast2"):
+            with rt.timers.comm("grad_w_summa_broadcast", be.wire(brow).numel() * 4, "comm_time", "summa_bcast2"):
                 _bcast(be.wire(brow), col_src, g.col_group)
         with rt.timers.region("comp_time", "summa_comp"):
             be.mm_tn_acc(acol, brow, z)
@@ -226,7 +229,8 @@ def gather_weight_blocks(model, block, f_in, f_out):
     padded = torch.zeros((max(f_sizes), max(o_sizes)), dtype=block.dtype, device=block.device)
     padded[:block.size(0), :block.size(1)] = block
     parts = [torch.empty_like(padded) for _ in range(q * q)]
-    dist.all_gather(parts, padded, group=g.group)
+    with model.rt.timers.comm("grad_w_all_gather", all_gather_bytes(padded.numel() * 4, q * q)):
+        dist.all_gather(parts, padded, group=g.group)
     rows = []
     for i in range(q):
         rows.append(torch.cat([parts[i * q + j][:f_sizes[i], :o_sizes[j]] for j in range(q)], dim=1))
@@ -238,10 +242,12 @@ def dist_log_softmax(model, z):
     g, be = model.grid, model.rt.backend
     m = be.row_max(z)
     if g.comm:
-        dist.all_reduce(m, op=dist.ReduceOp.MAX, group=g.row_group)
+        with model.rt.timers.comm("log_softmax_all_reduce", all_reduce_bytes(m.numel() * 4, g.q)):
+            dist.all_reduce(m, op=dist.ReduceOp.MAX, group=g.row_group)
     s = be.row_sumexp(z, m)
     if g.comm:
-        dist.all_reduce(s, op=dist.ReduceOp.SUM, group=g.row_group)
+        with model.rt.timers.comm("log_softmax_all_reduce", all_reduce_bytes(s.numel() * 4, g.q)):
+            dist.all_reduce(s, op=dist.ReduceOp.SUM, group=g.row_group)
     return be.log_softmax_apply(z, m, s)
 
 
@@ -250,7 +256,8 @@ def dist_log_softmax_bwd(model, logp, grad):
     g, be = model.grid, model.rt.backend
     rs = be.row_sum(grad)
     if g.comm:
-        dist.all_reduce(rs, op=dist.ReduceOp.SUM, group=g.row_group)
+        with model.rt.timers.comm("log_softmax_all_reduce", all_reduce_bytes(rs.numel() * 4, g.q)):
+            dist.all_reduce(rs, op=dist.ReduceOp.SUM, group=g.row_group)
     return be.log_softmax_bwd_apply(logp, grad, rs)
 
 

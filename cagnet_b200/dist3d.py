@@ -21,7 +21,7 @@ from . import partition
 from .backend import ACT_LOG_SOFTMAX, ACT_NONE, ACT_RELU
 from .dist1d import Data, act_name  # noqa: F401
 from .dist2d import MaskedNLL, _bcast, _offsets
-from .timing import CATEGORIES_3D, Timers
+from .timing import CATEGORIES_3D, Timers, all_gather_bytes, all_reduce_bytes
 
 
 class Runtime:
@@ -87,7 +87,7 @@ def split3dspmm_sparse(model, inputs):
         src = g.rank_of(g.i, kp, g.k)
         if src == g.rank:
             if g.comm and not (rt.cache_blocks and model.blocks_sent):
-                with rt.timers.region("comm_time", "summa_sparse_bcast1"):
+                with rt.timers.comm("a_block_broadcast", model.adj_wire.numel() * 4, "comm_time", "summa_sparse_bcast1"):
                     _bcast(model.adj_wire, src, g.row_group)
                 rt.timers.count("summa_sparse_bcast1_words", model.adj_wire.numel())
             return model.adj_block
@@ -95,7 +95,7 @@ def split3dspmm_sparse(model, inputs):
             return model.block_cache[kp]
         n_r, n_c, nnz = model.row_sizes[g.i], model.sub_sizes[kp][g.k], model.nnz_of[src]
         buf = be.wire_buffer(n_r, nnz)
-        with rt.timers.region("comm_time", "summa_sparse_bcast1"):
+        with rt.timers.comm("a_block_broadcast", buf.numel() * 4, "comm_time", "summa_sparse_bcast1"):
             _bcast(buf, src, g.row_group)
         rt.timers.count("summa_sparse_bcast1_words", buf.numel())
         blk = be.block_from_wire(buf, n_r, n_c, nnz, reused=rt.cache_blocks)
@@ -113,6 +113,8 @@ def split3dspmm_sparse(model, inputs):
                 bufs[kp % 2] = be.empty(model.max_sub, f_j)
             tensor = bufs[kp % 2][:rows]
         rt.timers.count("summa_sparse_bcast2_words", rows * f_j)
+        if g.comm:
+            rt.timers.traffic("h_broadcast", be.wire(tensor).numel() * 4)
         work = _bcast(be.wire(tensor), src, g.col_group, async_op=True) if g.comm else None
         return tensor, work
 
@@ -121,7 +123,7 @@ def split3dspmm_sparse(model, inputs):
     for kp in range(q):
         blk = a_slab(kp)
         if serial:
-            with rt.timers.region("comm_time", "summa_sparse_bcast2"):
+            with rt.timers.region("comm_time", "summa_sparse_bcast2", "link:h_broadcast"):
                 tensor, work = post_h(kp)
                 if work is not None:
                     work.wait()
@@ -134,7 +136,8 @@ def split3dspmm_sparse(model, inputs):
             be.spmm(blk, tensor, z, 0.0 if kp == 0 else 1.0)
     model.blocks_sent = True
     if g.comm:
-        with rt.timers.region("comm_time", "summa_sparse_reduce"):
+        with rt.timers.comm("z_fiber_all_reduce", all_reduce_bytes(be.wire(z).numel() * 4, q), "comm_time",
+                            "summa_sparse_reduce"):
             dist.all_reduce(be.wire(z), group=g.fiber_group)
     return _column_chunk(be, z, partition.chunk_sizes(f_j, q), g.k)
 
@@ -159,7 +162,7 @@ def split3dspmm_loc(model, mata, weight, transposed):
         src = g.rank_of(g.i, kp, g.k)
         acol = mata if src == g.rank else be.empty(n_i, k_sizes[kp][g.k])
         if g.comm:
-            with rt.timers.region("comm_time", "summa_loc_bcast"):
+            with rt.timers.comm("z_block_broadcast", be.wire(acol).numel() * 4, "comm_time", "summa_loc_bcast"):
                 _bcast(be.wire(acol), src, g.row_group)
         c0, c1 = ko[kp * q + g.k], ko[kp * q + g.k + 1]
         part = w[oo[g.j]:oo[g.j + 1], c0:c1] if transposed else w[c0:c1, oo[g.j]:oo[g.j + 1]]
@@ -169,7 +172,8 @@ def split3dspmm_loc(model, mata, weight, transposed):
             else:
                 be.mm_acc(acol, part, z, trans_w=transposed)
     if g.comm:
-        with rt.timers.region("comm_time", "summa_reduce"):
+        with rt.timers.comm("zw_fiber_all_reduce", all_reduce_bytes(be.wire(z).numel() * 4, q), "comm_time",
+                            "summa_reduce"):
             dist.all_reduce(be.wire(z), group=g.fiber_group)
     ro = _offsets(model.sub_sizes[g.i])
     return be.as_matrix(z[ro[g.k]:ro[g.k + 1]])
@@ -188,7 +192,8 @@ def transpose(model, ag, out_total):
         padded = torch.zeros((n_i, max(widths)), dtype=torch.float32, device=ag.device)
         padded[:, :ag.size(1)] = ag
         parts = [torch.empty_like(padded) for _ in range(q)]
-        dist.all_gather(parts, padded, group=g.fiber_group)
+        with model.rt.timers.comm("transpose_all_gather", all_gather_bytes(padded.numel() * 4, q)):
+            dist.all_gather(parts, padded, group=g.fiber_group)
         full = torch.cat([parts[k][:, :widths[k]] for k in range(q)], dim=1)
     else:
         full = ag
@@ -199,8 +204,9 @@ def transpose(model, ag, out_total):
     peer = g.rank_of(g.j, g.i, g.k)
     recv = be.empty(model.sub_sizes[g.j][g.k], o_sizes[g.i])
     ops = [dist.P2POp(dist.isend, be.wire(mine), peer), dist.P2POp(dist.irecv, be.wire(recv), peer)]
-    for work in dist.batch_isend_irecv(ops):
-        work.wait()
+    with model.rt.timers.comm("transpose_exchange", be.wire(recv).numel() * 4):
+        for work in dist.batch_isend_irecv(ops):
+            work.wait()
     return recv
 
 
@@ -217,14 +223,14 @@ def split3dspmm_tn(model, ag_t, inputs, f_in, f_out):
         acol = ag_t if row_src == g.rank else be.empty(rows, o_sizes[g.i])
         brow = inputs if col_src == g.rank else be.empty(rows, f_sizes[g.j])
         if g.comm:
-            with rt.timers.region("comm_time", "summa_bcast1"):
+            with rt.timers.comm("grad_w_summa_broadcast", be.wire(acol).numel() * 4, "comm_time", "summa_bcast1"):
                 _bcast(be.wire(acol), row_src, g.row_group)
-            with rt.timers.region("comm_time", "summa_bcast2"):
+            with rt.timers.comm("grad_w_summa_broadcast", be.wire(brow).numel() * 4, "comm_time", "summa_bcast2"):
                 _bcast(be.wire(brow), col_src, g.col_group)
         with rt.timers.region("comp_time", "summa_comp"):
             be.mm_tn_acc(brow, acol, z)
     if g.comm:
-        with rt.timers.region("comm_time", "summa_reduce"):
+        with rt.timers.comm("grad_w_fiber_all_reduce", all_reduce_bytes(z.numel() * 4, q), "comm_time", "summa_reduce"):
             dist.all_reduce(z, group=g.fiber_group)
     return z
 
@@ -239,7 +245,8 @@ def gather_weight_blocks(model, block, f_in, f_out):
     padded = torch.zeros((max(f_sizes), max(o_sizes)), dtype=block.dtype, device=block.device)
     padded[:block.size(0), :block.size(1)] = block
     parts = [torch.empty_like(padded) for _ in range(g.size)]
-    dist.all_gather(parts, padded, group=g.group)
+    with model.rt.timers.comm("grad_w_all_gather", all_gather_bytes(padded.numel() * 4, g.size)):
+        dist.all_gather(parts, padded, group=g.group)
     rows = []
     for j in range(q):
         rows.append(torch.cat([parts[g.rank_of(i, j, 0)][:f_sizes[j], :o_sizes[i]] for i in range(q)], dim=1))
@@ -250,10 +257,12 @@ def dist_log_softmax(model, z):
     g, be = model.grid, model.rt.backend
     m = be.row_max(z)
     if g.comm:
-        dist.all_reduce(m, op=dist.ReduceOp.MAX, group=g.row_group)
+        with model.rt.timers.comm("log_softmax_all_reduce", all_reduce_bytes(m.numel() * 4, g.q)):
+            dist.all_reduce(m, op=dist.ReduceOp.MAX, group=g.row_group)
     s = be.row_sumexp(z, m)
     if g.comm:
-        dist.all_reduce(s, op=dist.ReduceOp.SUM, group=g.row_group)
+        with model.rt.timers.comm("log_softmax_all_reduce", all_reduce_bytes(s.numel() * 4, g.q)):
+            dist.all_reduce(s, op=dist.ReduceOp.SUM, group=g.row_group)
     return be.log_softmax_apply(z, m, s)
 
 
@@ -261,7 +270,8 @@ def dist_log_softmax_bwd(model, logp, grad):
     g, be = model.grid, model.rt.backend
     rs = be.row_sum(grad)
     if g.comm:
-        dist.all_reduce(rs, op=dist.ReduceOp.SUM, group=g.row_group)
+        with model.rt.timers.comm("log_softmax_all_reduce", all_reduce_bytes(rs.numel() * 4, g.q)):
+            dist.all_reduce(rs, op=dist.ReduceOp.SUM, group=g.row_group)
     return be.log_softmax_bwd_apply(logp, grad, rs)
 
 

@@ -138,8 +138,8 @@ def _row_major(t):
 # how many rectangles may be cut out one after the other (a second one, 9,216 x 4,096 at 30 % density on the
 # benchmark graph, measured no gain: 13.30 ms against 13.13 ms).
 # "tensor_cores": multiply the core with the tcgen05 kernel when the library was built with it (fp32 accuracy
-# through a three-term bf16 split, 123 TFLOP/s against 40 for the fp32-FMA kernel); a dense cell then costs a
-# twelfth of a gathered nonzero and "density_tc" is the bar instead of "density".
+# through the hi/lo TF32 split, "3xTF32": 172 TFLOP/s fp32-equivalent against 40 for the fp32-FMA kernel); a dense
+# cell then costs a twelfth of a gathered nonzero and "density_tc" is the bar instead of "density".
 CORE = {"enabled": os.environ.get("CAGNET_DENSE_CORE", "1") != "0", "density": 0.2, "density_tc": 0.09, "step": 1024,
         "max_side": 16384, "max_bytes": 2 << 30, "min_share": 0.1, "min_width": 128, "rounds": 1,
         "tensor_cores": os.environ.get("CAGNET_CORE_TENSOR", "1") != "0"}
@@ -329,15 +329,27 @@ def _core_multiply(dense, core_rows, core_cols, split, B, ldb, C, ldc, f):
     LAUNCHES[0] += 2 if nbytes else 1      # the multiply and the pass that adds up its k slices
 
 
-def spmm_gpu(A_rowindices, A_colindices, A_values, n, m, B, C):
+SPMM_GPU_VALIDATE = os.environ.get("CAGNET_SPMM_GPU_VALIDATE", "1") != "0"
+
+
+def spmm_gpu(A_rowindices, A_colindices, A_values, n, m, B, C, validate=None):
     """Drop-in for `sparse_coo_tensor_cpp.spmm_gpu` (sparse_coo_tensor.cu:113-119): C += A.B in place, A given
-    as row-sorted COO with int32 indices.  Value semantics only: strides of B and C are left untouched, there
-    is no device-wide synchronisation, and the work is queued on the current stream."""
+    as row-sorted COO with int32 indices.  Value semantics only: strides of B and C are left untouched, exactly
+    the n x f elements of C change, and the work is queued on the current stream.
+
+    The indices are checked on the device first (sorted rows, rows in [0, n), columns in [0, m)): one 4-byte
+    readback, i.e. one stream synchronisation per call where the reference op synchronises the whole device
+    (sparse_coo_tensor.cu:231); an out-of-range column would otherwise be an out-of-bounds gather.
+    `validate=False` (or CAGNET_SPMM_GPU_VALIDATE=0) skips the check and the synchronisation for callers whose
+    indices are known to be good."""
     if A_rowindices.dtype != torch.int32 or A_colindices.dtype != torch.int32:
         raise RuntimeError("cagnet_b200: spmm_gpu expects int32 indices (call .int() as the reference does)")
     if n > _INT32_MAX or m > _INT32_MAX:
         raise RuntimeError("cagnet_b200: spmm_gpu block does not fit 32-bit indices")
-    block = CsrBlock(coo2csr(A_rowindices, n), A_colindices.contiguous(), A_values.float().contiguous(), n, m)
+    rows32 = A_rowindices.contiguous()
+    block = CsrBlock(coo2csr(rows32, n), A_colindices.contiguous(), A_values.float().contiguous(), n, m)
+    if SPMM_GPU_VALIDATE if validate is None else validate:
+        block.validate(rows32)
     block.build_plan(core=False)      # a per-call block: the core split only pays when it is reused
     Bc = B if _row_major(B) else B.contiguous()
     if _row_major(C):

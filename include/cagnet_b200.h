@@ -46,7 +46,10 @@ const char* cagnet_last_error_string(void);
  * two-vectors-per-lane mapping for products of 5..16 vectors), "spmm_rpb" (rows per thread block of the
  * warp-per-row kernel), "spmm_long" (rows with more nonzeros than this are listed in the plan and processed by a
  * whole thread block), "spmm_long_narrow" (a lower bound on that limit for products narrower than 128 columns;
- * equal to "spmm_long" by default), "core_chunk" (k length of one tensor-core accumulation of the dense-core
+ * equal to "spmm_long" by default), "spmm_group_avg" (blocks with at most this many nonzeros per row on average run
+ * the lane-group kernel when B is narrower than 128 columns; 0 = never) and "spmm_group_max" (rows up to this length
+ * are walked by one lane group there, longer ones by the whole warp; "spmm_group_pool" = consecutive rows per warp,
+ * 0 = automatic), "core_chunk" (k length of one tensor-core accumulation of the dense-core
  * multiply, a multiple of 32).  Host-side global state; returns CAGNET_E_ARG for an unknown name or value. */
 int cagnet_set_param(const char* name, int value);
 int cagnet_get_param(const char* name);
@@ -75,7 +78,8 @@ int cagnet_spmm_plan_i32(const int32_t* rowptr, int32_t n, int64_t nnz, void* pl
  * beta is 0 (overwrite) or 1 (accumulate, the reference's in-place `C += A.B`).
  * `plan` may be NULL (every row is then processed by one warp).  If ldb and ldc are multiples of 4
  * (2) and B, C are 16-byte (8-byte) aligned the kernel moves 128-bit (64-bit) vectors; columns
- * [f, ld) of such padded rows may be read and overwritten with unspecified values.
+ * [f, ld) of such padded rows of B and C may be read, and are never written: exactly n x f elements of C change,
+ * as with the reference op, so C may be a column slice of a wider matrix.
  * Replaces cusparseSpMM(alpha=1, beta=1, CSRMM_ALG1) plus the row/column-major re-layouts around
  * it at sparse-extension/sparse_coo_tensor.cu:149-226. */
 int cagnet_spmm_csr_f32(const int32_t* rowptr, const int32_t* col, const float* val,
@@ -93,7 +97,10 @@ int cagnet_spmm_csr_f32(const int32_t* rowptr, const int32_t* col, const float* 
  *   - Limit: nnz <= cagnet_spmm_noalloc_max_nnz() (65,535 x the hub-row threshold: about 134 M at the default
  *     2048); beyond it the call returns CAGNET_E_WORKSPACE and does nothing.
  *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that
- *     device current); make that first call before starting any stream capture.
+ *     device current; `stream` must belong to it).  Under CUDA's lazy module loading that look-up is also the
+ *     moment the library's device code and this array are loaded onto the GPU, so "allocates nothing" holds from
+ *     the second call on: make one warm-up call per device at start-up, before any stream capture and before
+ *     the other allocator takes the rest of the memory.
  *   - All calls share the one array and the array keeps the last call's list: each call resets it first, and
  *     two calls whose kernels can overlap on the GPU (different streams, different host threads) race on it.
  *     Serialise them, or use cagnet_spmm_csr_f32 with one plan per block. */

@@ -11,7 +11,7 @@ from tests.mp_util import run_ranks
 
 
 def _worker(rank, world, case_path, replication, activations, normalization, overlap, order="reference",
-            stage_groups=2, collective="all_gather"):
+            stage_groups=2, collective="all_gather", prefetch=False):
     import numpy as np
     import torch
     from cagnet_b200 import dist1d, graphs
@@ -22,7 +22,7 @@ def _worker(rank, world, case_path, replication, activations, normalization, ove
     edge, x, y, mask = (torch.from_numpy(d[k]) for k in ("edge_index", "x", "y", "mask"))
     adj = graphs.add_self_loops(edge, n) if normalization else edge
     rt = dist1d.Runtime(CpuBackend(), activations, normalization, replication, timing=False, overlap=overlap,
-                        order=order, stage_groups=stage_groups, collective=collective)
+                        order=order, stage_groups=stage_groups, collective=collective, prefetch_features=prefetch)
     group, row_groups, col_groups = dist1d.make_groups(rank, world, replication)
     model = dist1d.Model(rt, rank, world, x, adj, dist1d.Data(y=y, train_mask=mask), f, classes, group, row_groups,
                          col_groups)
@@ -35,7 +35,27 @@ def _worker(rank, world, case_path, replication, activations, normalization, ove
         out[f"ep{ep}_gw2"] = model.weight2.grad.numpy().copy()
         out[f"ep{ep}_w1"] = model.weight1.detach().numpy().copy()
         out[f"ep{ep}_w2"] = model.weight2.detach().numpy().copy()
+    out["links"] = {k: list(v) for k, v in rt.timers.links.items()}
     return out
+
+
+@pytest.mark.parametrize("groups", [1, 2])
+def test_feature_prefetch_gives_the_same_epochs(golden_dir, groups):
+    """The layer-1 all-gather of epoch k+1 posted during epoch k (own communicator, second buffer set) changes no
+    number, and the same bytes are booked per epoch as without it (one gather more: the last one is never read)."""
+    path = os.path.join(golden_dir, "train_1d_P3.npz")
+    d = np.load(path)
+    n, f, mid, classes, epochs, P, c, norm, act = d["cfg"].tolist()
+    plain = run_ranks(P, _worker, path, c, True, True, True, "reference", groups, "all_gather", False)
+    pre = run_ranks(P, _worker, path, c, True, True, True, "reference", groups, "all_gather", True)
+    for rank in range(P):
+        for ep in range(epochs):
+            for key in ("out", "gw1", "gw2", "w1", "w2"):
+                np.testing.assert_array_equal(pre[rank][f"ep{ep}_{key}"], plain[rank][f"ep{ep}_{key}"])
+                np.testing.assert_allclose(pre[rank][f"ep{ep}_{key}"], d[f"r{rank}_ep{ep}_{key}"], rtol=1e-4, atol=2e-5)
+        a, b = plain[rank]["links"]["h_all_gather"], pre[rank]["links"]["h_all_gather"]
+        assert b[0] == a[0] + groups and b[1] > a[1]
+        assert plain[rank]["links"]["grad_w_all_reduce"][0] == 2 * epochs
 
 
 @pytest.mark.parametrize("name,overlap,groups,collective", [

@@ -94,6 +94,81 @@ def test_spmm_hub_rows_and_tilings(f, tile):
         _native.set_param("spmm_tile", old_tile)
 
 
+def _skewed_block(n, m, seed, hubs=2):
+    """Short rows of very different lengths (1 .. ~200 nonzeros, most of them a handful), a few empty ones and
+    `hubs` rows beyond the hub threshold: what an R-MAT block with edge factor 16 looks like to the kernels."""
+    g = torch.Generator().manual_seed(seed)
+    lens = (torch.rand(n, generator=g).pow(6) * 200).long() + (torch.rand(n, generator=g) < 0.9).long()
+    r = torch.repeat_interleave(torch.arange(n), lens)
+    c = torch.randint(0, m, (r.numel(),), generator=g)
+    for h in range(hubs):
+        extra = torch.randperm(m, generator=g)[: min(m, 3000)]
+        r = torch.cat([r, torch.full_like(extra, (13 * h + 1) % n)])
+        c = torch.cat([c, extra])
+    blk = PP.coalesce_block(r, c, n, m)
+    return PP.Block(blk.rows, blk.cols, torch.randn(blk.vals.numel(), generator=g), n, m)
+
+
+@pytest.mark.parametrize("f", [1, 3, 8, 16, 24, 41, 64, 100])
+@pytest.mark.parametrize("pool,group_max", [(0, 64), (4, 0), (8, 7), (16, 64), (32, 64), (32, 4096)])
+def test_spmm_lane_group_kernel(f, pool, group_max):
+    """Blocks with few nonzeros per row take the lane-group kernel below 128 columns: every pool size, rows routed
+    to a lane group or to the whole warp by length, hub rows left to the block-per-row kernel; beta 0 and 1; NaN in
+    the pad columns of B and C must not reach a result, and columns of C beyond f must keep their contents."""
+    names = ("spmm_group_pool", "spmm_group_max", "spmm_long")
+    old = {k: _native.get_param(k) for k in names}
+    try:
+        _native.set_param("spmm_group_pool", pool)
+        _native.set_param("spmm_group_max", group_max)
+        _native.set_param("spmm_long", 512)
+        blk = _skewed_block(2311, 3001, seed=f + pool)
+        assert blk.vals.numel() <= _native.get_param("spmm_group_avg") * blk.n_rows
+        A = ops.CsrBlock.from_coo(blk.rows, blk.cols, blk.vals, blk.n_rows, blk.n_cols)
+        assert A.long_rows() >= 2
+        g = torch.Generator().manual_seed(5 + f)
+        B = torch.randn(blk.n_cols, f, generator=g)
+        C0 = torch.randn(blk.n_rows, f, generator=g)
+        prod = torch.sparse.mm(_dense64(blk), B.double())
+        Bd = _poison_pads(ops.to_padded(B.cuda()))
+        for beta in (0.0, 1.0):
+            Cd = _poison_pads(ops.to_padded(C0.cuda()))
+            ops.spmm(A, Bd, Cd, beta)
+            _close(Cd, prod + (C0.double() if beta else 0))
+            ld = Cd.stride(0)
+            if ld > f:
+                assert bool(torch.isnan(ops.base_buffer(Cd).view(-1, ld)[:, f:]).all()), "pad columns of C were written"
+        Cd2 = ops.zeros_padded(blk.n_rows, f, "cuda")
+        ops.spmm(A, Bd, Cd2, 0.0)
+        Cd3 = ops.zeros_padded(blk.n_rows, f, "cuda")
+        ops.spmm(A, Bd, Cd3, 0.0)
+        assert torch.equal(Cd2, Cd3)                              # bit-reproducible whatever the claim order was
+    finally:
+        for k, v in old.items():
+            _native.set_param(k, v)
+
+
+@pytest.mark.parametrize("f", [3, 41, 130, 602])
+def test_spmm_writes_only_n_by_f(f):
+    """C may be a column slice of a wider matrix (same row stride): the columns next to it belong to the caller."""
+    for blk in (_random_block(500, 700, 8, seed=f), _random_block(300, 4000, 150, seed=f + 1, hubs=3)):
+        A = ops.CsrBlock.from_coo(blk.rows, blk.cols, blk.vals, blk.n_rows, blk.n_cols)
+        g = torch.Generator().manual_seed(f)
+        B = torch.randn(blk.n_cols, f, generator=g)
+        wide = ops.pad_ld(f) + 4
+        Z0 = torch.randn(blk.n_rows, wide, generator=g)
+        Z = Z0.cuda().clone()
+        C = Z[:, :f]
+        want = Z0[:, :f].double() + torch.sparse.mm(_dense64(blk), B.double())
+        ops.spmm(A, ops.to_padded(B.cuda()), C, 1.0)
+        _close(Z[:, :f], want)
+        assert torch.equal(Z[:, f:].cpu(), Z0[:, f:]), "columns beyond f were modified"
+        Z = Z0.cuda().clone()
+        ops.spmm_gpu(blk.rows.int().cuda(), blk.cols.int().cuda(), blk.vals.cuda(), blk.n_rows, blk.n_cols, B.cuda(),
+                     Z[:, :f])
+        _close(Z[:, :f], want)
+        assert torch.equal(Z[:, f:].cpu(), Z0[:, f:])
+
+
 def test_spmm_is_bit_reproducible():
     blk = _random_block(3000, 3000, 30, seed=8, hubs=3)
     A = ops.CsrBlock.from_coo(blk.rows, blk.cols, blk.vals, blk.n_rows, blk.n_cols)
