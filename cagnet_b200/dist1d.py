@@ -393,7 +393,10 @@ class Model:
         self.group, self.row_groups, self.col_groups = group, row_groups, col_groups
         node_count = inputs.size(0)
         self.node_count = node_count
-        inputs_loc, blocks = partition.oned_partition(rank, size, inputs, adj_matrix, rt.normalization, c)
+        # degrees: every rank counts 1/P of the edge list, one all-reduce (all ranks hold the same list and are here)
+        everyone = group if (group is not None and size % c == 0) else None
+        inputs_loc, blocks = partition.oned_partition(rank, size, inputs, adj_matrix, rt.normalization, c,
+                                                      degree_group=everyone)
         self.inputs_loc = be.as_matrix(inputs_loc)
         n_per_proc = int(math.ceil(float(node_count) / (size / c)))
         # automatic launch groups: one.  Two groups put the communication of the second under the multiply of the

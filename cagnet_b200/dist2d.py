@@ -329,7 +329,9 @@ class Model:
         n = inputs.size(0)
         self.node_count = n
         self.row_sizes = partition.chunk_sizes(n, q)
-        inputs_loc, block = partition.twod_partition(rank, size, inputs, adj_matrix, rt.normalization)
+        everyone = g.group if (g.comm and q * q == size) else None
+        inputs_loc, block = partition.twod_partition(rank, size, inputs, adj_matrix, rt.normalization,
+                                                     degree_group=everyone)
         self.inputs_loc = be.as_matrix(inputs_loc)
         self.adj_block = be.make_block(block)
         self.adj_wire = be.block_to_wire(self.adj_block) if g.comm else None

@@ -326,7 +326,8 @@ class Model:
         self.row_sizes = partition.chunk_sizes(n, q)
         self.sub_sizes = [partition.chunk_sizes(s, q) for s in self.row_sizes]
         self.max_sub = max(max(s) for s in self.sub_sizes)
-        inputs_loc, slab = partition.threed_partition(rank, size, inputs, adj_matrix, rt.normalization)
+        inputs_loc, slab = partition.threed_partition(rank, size, inputs, adj_matrix, rt.normalization,
+                                                      degree_group=g.group if g.comm else None)
         self.inputs_loc = be.as_matrix(inputs_loc)
         self.adj_block = be.make_block(slab)
         self.adj_wire = be.block_to_wire(self.adj_block) if g.comm else None

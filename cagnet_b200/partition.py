@@ -10,6 +10,8 @@ import math
 from typing import NamedTuple
 
 import torch
+import torch.distributed as dist
+
 
 
 class Block(NamedTuple):
@@ -37,12 +39,23 @@ def boundaries(node_count, n_per_proc, keep=None):
     return starts + [node_count]
 
 
-def inv_sqrt_degree(adj, node_count):
+def inv_sqrt_degree(adj, node_count, group=None):
     """deg^-1/2 in fp64 then rounded to fp32, deg = occurrences as a row index in the whole edge list.
     The reference takes `histc(rows, bins=n)` (gcn_distr.py:440), which equals this count whenever
-    vertices 0 and n-1 occur -- always the case once self loops are added."""
-    deg = torch.bincount(adj[0], minlength=node_count).double()
-    return deg.pow(-0.5).float()
+    vertices 0 and n-1 occur -- always the case once self loops are added.
+
+    With `group` (a process group whose members all hold the same edge list in the same order and all make this
+    call) every member counts its own 1/P slice of the list and one all-reduce of the int64 counts gives the
+    degrees: the same integers as the reference's count over the whole list on every rank, at 1/P of the scan."""
+    rows = adj[0]
+    if group is not None and dist.is_initialized() and dist.get_world_size(group) > 1:
+        size, rank = dist.get_world_size(group), dist.get_rank(group)
+        per = -(-rows.numel() // size)
+        deg = torch.bincount(rows[rank * per:(rank + 1) * per], minlength=node_count)
+        dist.all_reduce(deg, group=group)
+    else:
+        deg = torch.bincount(rows, minlength=node_count)
+    return deg.double().pow(-0.5).float()
 
 
 def coalesce_block(r, c, n_rows, n_cols, d_row=None, d_col=None):
@@ -80,7 +93,7 @@ def _in_range(x, lo, hi):
 
 
 # ------------------------------------------------------------------------------------------ 1D / 1.5D
-def oned_partition(rank, size, inputs, adj, normalization=True, replication=1):
+def oned_partition(rank, size, inputs, adj, normalization=True, replication=1, degree_group=None):
     """Blocks and feature rows of one rank for the 1D (replication = 1, gcn_distr.py:472-522) and 1.5D
     (gcn_distr_15d.py:497-549) algorithms.  blocks[i] is what the layer multiplies by H_i: the
     transpose of A[rows_i, cols_rank], coalesced (gcn_distr.py:546), n_rank x n_i."""
@@ -89,7 +102,7 @@ def oned_partition(rank, size, inputs, adj, normalization=True, replication=1):
     rank_c = rank // replication
     vtx = boundaries(n, n_per_proc)
     lo, hi = vtx[rank_c], vtx[rank_c + 1]
-    d = inv_sqrt_degree(adj, n) if normalization else None
+    d = inv_sqrt_degree(adj, n, degree_group) if normalization else None
     sel = _in_range(adj[1], lo, hi)
     u, v = adj[0][sel], adj[1][sel] - lo
     blocks = []
@@ -128,7 +141,7 @@ def grid_side_2d(size):
     return math.floor(math.sqrt(size))
 
 
-def twod_partition(rank, size, inputs, adj, normalization=True, q=None):
+def twod_partition(rank, size, inputs, adj, normalization=True, q=None, degree_group=None):
     """Block (rank_row, rank_col) of A -- not transposed -- and of H (rows and feature columns floor-split,
     remainder last): gcn_distr_2d.py:1093-1164."""
     n = inputs.size(0)
@@ -139,7 +152,7 @@ def twod_partition(rank, size, inputs, adj, normalization=True, q=None):
     sel = _in_range(adj[0], r0, r1) & _in_range(adj[1], c0, c1)
     u, v = adj[0][sel] - r0, adj[1][sel] - c0
     if normalization:
-        d = inv_sqrt_degree(adj, n)
+        d = inv_sqrt_degree(adj, n, degree_group)
         block = coalesce_block(u, v, r1 - r0, c1 - c0, d[r0:r1], d[c0:c1])
     else:
         block = coalesce_block(u, v, r1 - r0, c1 - c0)
@@ -169,13 +182,13 @@ def coords_3d(rank, q):
     return (rank // q) // q, (rank // q) % q, rank % q
 
 
-def threed_partition(rank, size, inputs, adj, normalization=False):
+def threed_partition(rank, size, inputs, adj, normalization=False, degree_group=None):
     """2D block (i, j), then its columns cut into c slabs and the H block's rows into c chunks; this rank keeps
     slab / chunk k (gcn_distr_3d.py:1533-1542, 1341-1382).  The reference never normalises here
     (gcn_distr_3d.py:66); `normalization=True` is this package's extension and scales exactly as 2D does."""
     q = grid_side_3d(size)
     i, j, k = coords_3d(rank, q)
-    inputs_2d, blk = twod_partition(i * q + j, q * q, inputs, adj, normalization, q=q)
+    inputs_2d, blk = twod_partition(i * q + j, q * q, inputs, adj, normalization, q=q, degree_group=degree_group)
     vtx = boundaries(blk.n_cols, blk.n_cols // q, keep=q)
     s = _in_range(blk.cols, vtx[k], vtx[k + 1])
     # the reference rebuilds the slab from the coalesced indices with unit values (gcn_distr_3d.py:1357-1364)
