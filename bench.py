@@ -71,9 +71,9 @@ def dense_core_info(model):
         blk = model.am_pbyp.groups[0].block
         if blk.core is None:
             return None
-        dense = blk.core[0]
-        return {"rows": int(dense.size(0)), "cols": int(dense.size(1)), "nnz": int(blk.nnz - blk.rest.nnz),
-                "tensor_cores": blk.core_split is not None}
+        rows, cols = blk.core_shape()
+        return {"rows": rows, "cols": cols, "nnz": int(blk.nnz - blk.rest.nnz), "kind": blk.core_kind(),
+                "tensor_cores": blk.core_kind() in ("bf16-integer", "3xtf32")}
     except (AttributeError, IndexError):      # an informational field must not cost the line
         return None
 
@@ -585,7 +585,8 @@ def run_algorithm(ctx, algo, args, workload, x, adj, data, f, classes, info):
         flops = sum(2.0 * r[2] * r[3] for r in wide) / max(len(wide), 1)
         core_kernel = None
         if dense_core_info(model) is not None:
-            core_kernel = "tcgen05" if dense_core_info(model)["tensor_cores"] else "sgemm"
+            core_kernel = {"bf16-integer": "tcgen05 kind::f16 (bf16 multiplicities x 3 bf16 terms)",
+                           "3xtf32": "tcgen05 kind::tf32 (3xTF32)", "fp32-fma": "sgemm"}[dense_core_info(model)["kind"]]
         line = {
             "metric": METRIC, "value": ms_per_step, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": False, "scaling": "strong",
@@ -597,7 +598,7 @@ def run_algorithm(ctx, algo, args, workload, x, adj, data, f, classes, info):
             "spmm_ms_by_width": {str(k): sum(v) / args.steps for k, v in sorted(per_width.items())},
             "roofline": {"bound": "hbm",
                          "kernel": "spmm f=%d on rank 0 (hub-row and warp-per-row / lane-group launches on the sparse part; "
-                                   "gather+split, tcgen05 3xTF32 multiplies in k chunks and row-add launches on a dense core)" % f_wide,
+                                   "gather+split, tcgen05 multiplies in k chunks and row-add launches on a dense core)" % f_wide,
                          "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak if peak else None,
                          "peak_source": peak_kind, "launch_ms": launch_ms, "calls_per_epoch": calls,
                          "traffic": spmm_traffic_bytes() if (world == 1 and args.workload == "cfg2" and algo == "1d") else None,

@@ -32,6 +32,11 @@ PROTOTYPES = {
     "cagnet_gather_split_rows_f32": (_i32, [_vp, _i64, _vp, _i32, _i32, _vp, _i64, _vp]),
     "cagnet_core_gemm_tc_f32": (_i32, [_vp, _vp, _i64, _i32, _i32, _vp, _i64, _vp, _i32, _vp, _sz, _vp]),
     "cagnet_add_rows3_f32": (_i32, [_vp, _i64, _vp, _i32, _i32, _vp, _i64, _vp]),
+    "cagnet_core_gemm_int_available": (_i32, []),
+    "cagnet_core_gemm_int_workspace_bytes": (_sz, [_i32, _i32, _i32]),
+    "cagnet_gather_scale_split3_bf16": (_i32, [_vp, _i64, _vp, _vp, _i32, _i32, _vp, _i64, _vp]),
+    "cagnet_core_gemm_int_bf16": (_i32, [_vp, _i64, _i32, _i32, _vp, _i64, _vp, _i32, _vp, _sz, _vp]),
+    "cagnet_add_rows_scaled3_f32": (_i32, [_vp, _i64, _vp, _vp, _i32, _i32, _vp, _i64, _vp]),
     "cagnet_gemm_nn_f32": (_i32, [_vp, _i64, _vp, _i64, _i32, _vp, _i64, _i64, _i32, _i32, _i32, _vp, _i64, _vp]),
     "cagnet_gemm_tn_workspace_bytes": (_sz, [_i64, _i32, _i32]),
     "cagnet_gemm_tn_f32": (_i32, [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _i32, _i32, _f32, _vp, _sz, _vp]),

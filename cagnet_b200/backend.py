@@ -35,7 +35,9 @@ class CudaBackend:
     # ---- sparse
     def make_block(self, block):
         """partition.Block (COO, any device) -> device CSR with its SpMM plan."""
-        return ops.CsrBlock.from_coo(block.rows, block.cols, block.vals, block.n_rows, block.n_cols)
+        return ops.CsrBlock.from_coo(block.rows, block.cols, block.vals, block.n_rows, block.n_cols,
+                                     row_scale=getattr(block, "row_scale", None),
+                                     col_scale=getattr(block, "col_scale", None))
 
     def block_shape(self, blk):
         return blk.n, blk.m

@@ -63,6 +63,10 @@ def build(force=False, verbose=False):
     headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))]
     headers.append(os.path.join(os.path.dirname(HERE), "include", "cagnet_b200.h"))
     cutlass = cutlass_include_dirs()
+    if not cutlass:
+        print("cagnet_b200.build: WARNING: no CUTLASS / CuTe header tree found (looked inside the flashinfer wheel): "
+              "the tcgen05 dense-core kernels are NOT built and the fp32-FMA core kernel is used instead",
+              file=sys.stderr, flush=True)
     srcs = sources()
     objs = [os.path.join(BUILD_DIR, os.path.basename(s)[:-3] + ".o") for s in srcs]
 
@@ -71,7 +75,7 @@ def build(force=False, verbose=False):
         if not force and not _stale(obj, [src] + headers):
             return ""
         extra = []
-        if os.path.basename(src) == "core_gemm_tc.cu" and cutlass:
+        if os.path.basename(src) in ("core_gemm_tc.cu", "core_gemm_int.cu") and cutlass:
             extra = ["--expt-relaxed-constexpr", "-DCAGNET_HAVE_CUTLASS", "-diag-suppress", "20012"]
             for d in cutlass:
                 extra += ["-I", d]

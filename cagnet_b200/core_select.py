@@ -32,7 +32,8 @@ class CoreChoice:
         self.inside, self.gain = inside, gain        # nonzeros in the rectangle; inside - bar * r * c
 
 
-def choose_core(rowptr, col, n, m, bar, step=1024, max_side=16384, max_bytes=2 << 30, min_share=0.03):
+def choose_core(rowptr, col, n, m, bar, step=1024, max_side=16384, max_bytes=2 << 30, min_share=0.03,
+                bytes_per_cell=4):
     """The best rectangle of a CSR block (rowptr: n + 1 offsets, col: column per nonzero), or None when no
     rectangle saves at least `min_share` of the block's nonzeros' worth of gathers."""
     nnz = int(col.numel())
@@ -58,7 +59,7 @@ def choose_core(rowptr, col, n, m, bar, step=1024, max_side=16384, max_bytes=2 <
     side_c = torch.arange(1, gc + 1, device=dev, dtype=torch.float64) * step
     cells = side_r[:, None] * side_c[None, :]
     gain = inside - float(bar) * cells
-    gain[cells * 4 > float(max_bytes)] = float("-inf")
+    gain[cells * float(bytes_per_cell) > float(max_bytes)] = float("-inf")
     best = int(torch.argmax(gain))
     i, j = divmod(best, gc)
     if not float(gain[i, j]) >= float(min_share) * nnz:
@@ -78,3 +79,23 @@ def split_core(col, val, n, choice):
     rest_rowptr = torch.zeros(n + 1, dtype=torch.int32, device=val.device)
     rest_rowptr[1:] = torch.cumsum(kept, 0).int()
     return dense, rest_rowptr, col[keep].contiguous(), val[keep].contiguous()
+
+
+def integer_core(dense, row_scale, col_scale, limit=256):
+    """The multiplicity matrix of a dense core whose block was scaled by two diagonals, or None.
+
+    `dense[i, j]` must equal fl32(row_scale[i] * fl32(cnt * col_scale[j])) bit for bit with cnt a non-negative
+    integer <= `limit` (the way partition.coalesce_block computes a normalised entry); then dense =
+    diag(row_scale) . cnt . diag(col_scale) and cnt is returned as an fp32 matrix.  Any cell that does not fit --
+    scales that do not belong to this block, weighted edges -- makes the answer None and the caller keeps the
+    fp32 values."""
+    outer = row_scale[:, None] * col_scale[None, :]
+    nz = dense != 0
+    cnt = torch.where(nz & (outer != 0), torch.round(dense / outer), torch.zeros_like(dense))
+    del outer
+    if float(cnt.max()) > limit or float(cnt.min()) < 0:
+        return None
+    back = row_scale[:, None] * (cnt * col_scale[None, :])
+    if not bool(torch.equal(back, dense)):
+        return None
+    return cnt

@@ -31,6 +31,7 @@ struct Tuning {
   int spmm_group_max = 64;      // lane-group kernel: rows up to this length are walked by one lane group
   int spmm_group_avg = 96;      // blocks with at most this many nonzeros per row on average use it (0 = never)
   int spmm_group_pool = 0;      // rows per warp pool there: 0 = automatic, else 4, 8, 16 or 32
+  int spmm_overlap = 1;         // the row kernel may start under the hub-row kernel's tail (programmatic launch)
 };
 static Tuning g_tuning;
 
@@ -97,6 +98,15 @@ __device__ __forceinline__ void store_row(float* __restrict__ cp, int column0, i
   }
 }
 
+// The hub-row kernel and the row kernel of one multiply write disjoint rows of C, so they may overlap: the hub
+// kernel's longest row (100K+ nonzeros in an R-MAT graph, one thread block) would otherwise be a tail during which
+// the rest of the GPU idles.  The row kernel is launched with programmatic stream serialisation: it may start as
+// soon as every block of the hub kernel has begun (`pdl_release_dependents`), and each of its threads waits for
+// the hub kernel to have completed before it exits (`pdl_wait_for_primary`), so that whatever follows in the stream
+// still sees both kernels finished.  Without a preceding hub kernel both are no-ops.
+__device__ __forceinline__ void pdl_release_dependents() { asm volatile("griddepcontrol.launch_dependents;"); }
+__device__ __forceinline__ void pdl_wait_for_primary() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // Accumulates sum_e val[e] * B[col[e], tile columns of this lane] over e in [start, end) into acc.
 // bt already points at column (tile0 + l*VEC) of row 0 of B; vector k of the lane sits k*LPN*VEC columns
 // further on and is live iff k < nvalid.
@@ -162,15 +172,10 @@ __device__ __forceinline__ void accumulate_range(const int* __restrict__ col, co
         }
       }
     } else {
-      // a short row or the tail of a long one: four predicated steps per trip keep several gathers in flight
-      for (int s = 0; s < cnt; s += 4 * G) {
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const int idx = s + u * G + sub;
-          if (idx < cnt) {
-            const int2 q = stage[idx];
-            gather(q.x, __int_as_float(q.y));
-          }
+      for (int s = 0; s < cnt; s += G) {
+        if (s + sub < cnt) {
+          const int2 q = stage[s + sub];
+          gather(q.x, __int_as_float(q.y));
         }
       }
     }
@@ -210,7 +215,10 @@ __global__ void __launch_bounds__(kMaxRowsPerBlock * 32) spmm_warp_rows_kernel(
   const int start = __ldg(rowptr + row);
   const int end = __ldg(rowptr + row + 1);
   const int long_threshold = plan ? max(__ldg(plan + 2), min_threshold) : INT_MAX;
-  if (end - start > long_threshold) return;  // a hub row: the block-per-row kernel owns it
+  if (end - start > long_threshold) {        // a hub row: the block-per-row kernel owns it
+    pdl_wait_for_primary();
+    return;
+  }
   const int nvalid = live_vectors<VEC, LPN, NV>(tile0, l, f_eff);
 
   float acc[NV][VEC];
@@ -223,6 +231,7 @@ __global__ void __launch_bounds__(kMaxRowsPerBlock * 32) spmm_warp_rows_kernel(
 
   if (lane < LPN)
     store_row<VEC, LPN, NV>(C + static_cast<int64_t>(row) * ldc + tile0 + l * VEC, tile0 + l * VEC, f, nvalid, beta, acc);
+  pdl_wait_for_primary();
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -265,8 +274,9 @@ __global__ void __launch_bounds__(kMaxRowsPerBlock * 32) spmm_group_rows_kernel(
   const int my_start = have ? __ldg(rowptr + row0 + lane) : 0;
   const int my_end = have ? __ldg(rowptr + row0 + lane + 1) : 0;
   const int my_len = my_end - my_start;
-  unsigned pending = __ballot_sync(0xffffffffu, have && my_len <= group_max);
-  unsigned medium = __ballot_sync(0xffffffffu, have && my_len > group_max && my_len <= long_threshold);
+  const int short_max = min(group_max, long_threshold);      // longer rows belong to the warp or to the hub kernel
+  unsigned pending = __ballot_sync(0xffffffffu, have && my_len <= short_max);
+  unsigned medium = __ballot_sync(0xffffffffu, have && my_len > short_max && my_len <= long_threshold);
 
   float acc[NV][VEC];
   int cur = -1, e = 0, e_end = 0;             // the group's row (pool index) and its nonzero cursor
@@ -348,6 +358,7 @@ __global__ void __launch_bounds__(kMaxRowsPerBlock * 32) spmm_group_rows_kernel(
     if (lane < LPN)
       store_row<VEC, LPN, NV>(C + static_cast<int64_t>(row0 + i) * ldc + column0, column0, f, nvalid, beta, acc);
   }
+  pdl_wait_for_primary();
 }
 
 template <int VEC, int LPN, int NV>
@@ -358,6 +369,7 @@ __global__ void __launch_bounds__(kLongWarps * 32) spmm_block_rows_kernel(
   constexpr int TILE = LPN * VEC * NV;
   __shared__ float part[kLongWarps][TILE];
   __shared__ __align__(16) int2 stage[kLongWarps][32];
+  pdl_release_dependents();
   const int long_threshold = max(__ldg(plan + 2), min_threshold);
   const int count = min(__ldg(plan + 1), __ldg(plan + 3));
   const int* list = plan + kPlanHeaderInts;
@@ -464,18 +476,38 @@ static int launch_spmm(const int* rowptr, const int* col, const float* val, int 
         rowptr, col, val, B, ldb, C, ldc, f_eff, f, beta, plan, min_threshold);
   }
   const int rows_per_block = g_tuning.spmm_rpb;
+  // the row kernel: allowed to start while the hub kernel's last rows are still running (see pdl_wait_for_primary)
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.blockDim = dim3(rows_per_block * 32);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = stream;
+  cfg.attrs = attr;
+  cfg.numAttrs = (plan && g_tuning.spmm_overlap) ? 1 : 0;
+  cudaError_t e;
+  bool grouped = false;
+  if constexpr (LPN < 32) grouped = g_tuning.spmm_group_avg > 0 && nnz <= static_cast<int64_t>(g_tuning.spmm_group_avg) * n;
   if constexpr (LPN < 32) {
-    if (g_tuning.spmm_group_avg > 0 && nnz <= static_cast<int64_t>(g_tuning.spmm_group_avg) * n) {
+    if (grouped) {
       const int pool = group_pool_rows(n);
       const int pools = (n + pool - 1) / pool;
-      spmm_group_rows_kernel<VEC, LPN, NV><<<dim3((pools + rows_per_block - 1) / rows_per_block, tiles),
-                                             rows_per_block * 32, 0, stream>>>(
-          rowptr, col, val, n, B, ldb, C, ldc, f_eff, f, beta, plan, min_threshold, g_tuning.spmm_group_max, pool);
-      return check_launch("cagnet_spmm_csr_f32");
+      cfg.gridDim = dim3((pools + rows_per_block - 1) / rows_per_block, tiles);
+      e = cudaLaunchKernelEx(&cfg, spmm_group_rows_kernel<VEC, LPN, NV>, rowptr, col, val, n, B, ldb, C, ldc, f_eff, f,
+                             beta, plan, min_threshold, g_tuning.spmm_group_max, pool);
     }
   }
-  spmm_warp_rows_kernel<VEC, LPN, NV><<<dim3((n + rows_per_block - 1) / rows_per_block, tiles), rows_per_block * 32, 0,
-                                        stream>>>(rowptr, col, val, n, B, ldb, C, ldc, f_eff, f, beta, plan, min_threshold);
+  if (!grouped) {
+    cfg.gridDim = dim3((n + rows_per_block - 1) / rows_per_block, tiles);
+    e = cudaLaunchKernelEx(&cfg, spmm_warp_rows_kernel<VEC, LPN, NV>, rowptr, col, val, n, B, ldb, C, ldc, f_eff, f, beta,
+                           plan, min_threshold);
+  }
+  if (e != cudaSuccess) {
+    snprintf(last_error_buf(), 256, "cagnet_spmm_csr_f32: CUDA launch failed: %s", cudaGetErrorString(e));
+    cudaGetLastError();
+    return CAGNET_E_LAUNCH;
+  }
   return check_launch("cagnet_spmm_csr_f32");
 }
 
@@ -560,6 +592,10 @@ extern "C" int cagnet_set_param(const char* name, int value) {
     g_tuning.spmm_group_pool = value;
     return CAGNET_OK;
   }
+  if (!strcmp(name, "spmm_overlap")) {
+    g_tuning.spmm_overlap = value != 0;
+    return CAGNET_OK;
+  }
   if (!strcmp(name, "spmm_group_avg")) {
     if (value < 0) return fail(CAGNET_E_ARG, "cagnet_set_param: spmm_group_avg must be >= 0");
     g_tuning.spmm_group_avg = value;
@@ -581,6 +617,7 @@ extern "C" int cagnet_get_param(const char* name) {
   if (name && !strcmp(name, "spmm_group_max")) return g_tuning.spmm_group_max;
   if (name && !strcmp(name, "spmm_group_avg")) return g_tuning.spmm_group_avg;
   if (name && !strcmp(name, "spmm_group_pool")) return g_tuning.spmm_group_pool;
+  if (name && !strcmp(name, "spmm_overlap")) return g_tuning.spmm_overlap;
   if (name && !strcmp(name, "core_chunk")) return core_chunk();
   return -1;
 }

@@ -143,7 +143,16 @@ class GatherPlan:
             c = torch.cat([p.cols for p in parts])
             v = torch.cat([p.vals for p in parts])
             order = torch.argsort(r * (size * rows) + c)
-            fused = partition.Block(r[order], c[order], v[order], self.n_loc, size * rows)
+            # the diagonal factors of the fused block: this rank's row factor, and per buffer position the column
+            # factor of the vertex that lands there (padding positions, which no column refers to, get 0)
+            row_scale = col_scale = None
+            if all(b.row_scale is not None and b.col_scale is not None for b in blocks):
+                row_scale = blocks[0].row_scale
+                col_scale = torch.zeros(size * rows, dtype=torch.float32, device=row_scale.device)
+                for i, b in enumerate(blocks):
+                    piece = b.col_scale[lo:hi]
+                    col_scale[i * rows:i * rows + piece.numel()] = piece
+            fused = partition.Block(r[order], c[order], v[order], self.n_loc, size * rows, row_scale, col_scale)
             self.groups.append(GatherGroup(lo, rows, backend.make_block(fused)))
 
 

@@ -140,13 +140,23 @@ def _row_major(t):
 # "tensor_cores": multiply the core with the tcgen05 kernel when the library was built with it (fp32 accuracy
 # through the hi/lo TF32 split, "3xTF32": 172 TFLOP/s fp32-equivalent against 40 for the fp32-FMA kernel); a dense
 # cell then costs a twelfth of a gathered nonzero and "density_tc" is the bar instead of "density".
+# "integer": a block that carries its normalisation factors (partition.Block.row_scale / col_scale) keeps its core
+# as the bf16 matrix of edge multiplicities between the two diagonals and multiplies it with three bf16 products
+# (csrc/core_gemm_int.cu): a quarter of the memory and a third of the tensor time of the 3xTF32 form, so the bar
+# is "density_int", the side limit "max_side_int", and products down to "min_width_int" columns use it.
 CORE = {"enabled": os.environ.get("CAGNET_DENSE_CORE", "1") != "0", "density": 0.2, "density_tc": 0.09, "step": 1024,
         "max_side": 16384, "max_bytes": 2 << 30, "min_share": 0.1, "min_width": 128, "rounds": 1,
-        "tensor_cores": os.environ.get("CAGNET_CORE_TENSOR", "1") != "0"}
+        "tensor_cores": os.environ.get("CAGNET_CORE_TENSOR", "1") != "0",
+        "integer": os.environ.get("CAGNET_CORE_INTEGER", "1") != "0", "density_int": 0.03, "max_side_int": 32768,
+        "min_width_int": 128}
 
 
 def core_on_tensor_cores():
     return bool(CORE["tensor_cores"]) and _native.lib().cagnet_core_gemm_tc_available() == 1
+
+
+def integer_core_available():
+    return bool(CORE["tensor_cores"]) and bool(CORE["integer"]) and _native.lib().cagnet_core_gemm_int_available() == 1
 
 
 def configure_core(**kw):
@@ -184,10 +194,13 @@ class CsrBlock:
         self.nnz = int(val.numel())
         self.core = self.rest = None      # dense hub-by-hub rectangle and the CSR block of everything else
         self.core_split = None            # the rectangle as TF32 hi + lo parts (tensor-core multiply)
+        self.core_int = None              # (bf16 multiplicities, rows, cols, row factors, column factors)
+        self.row_scale = self.col_scale = None    # the diagonals a normalised block was scaled with, if known
 
     @staticmethod
-    def from_coo(rows, cols, vals, n, m, validate=True, plan=True):
-        """rows/cols: integer tensors sorted by row (a coalesced COO), vals fp32; any device (moved to CUDA)."""
+    def from_coo(rows, cols, vals, n, m, validate=True, plan=True, row_scale=None, col_scale=None):
+        """rows/cols: integer tensors sorted by row (a coalesced COO), vals fp32; any device (moved to CUDA).
+        row_scale / col_scale: the diagonals of a normalised block (see partition.Block), optional."""
         if n > _INT32_MAX or m > _INT32_MAX or vals.numel() > _INT32_MAX:
             raise RuntimeError("cagnet_b200: block does not fit 32-bit indices")
         dev = vals.device if vals.is_cuda else torch.device("cuda", torch.cuda.current_device())
@@ -196,6 +209,9 @@ class CsrBlock:
         val = vals.to(device=dev, dtype=torch.float32).contiguous()
         rowptr = coo2csr(rows32, n)
         blk = CsrBlock(rowptr, col32, val, n, m)
+        if row_scale is not None and col_scale is not None:
+            blk.row_scale = row_scale.to(device=dev, dtype=torch.float32).contiguous()
+            blk.col_scale = col_scale.to(device=dev, dtype=torch.float32).contiguous()
         if validate:
             blk.validate(rows32)
         if plan:
@@ -243,26 +259,65 @@ class CsrBlock:
         cfg = CORE
         if not cfg["enabled"]:
             return
-        bar = cfg["density_tc"] if core_on_tensor_cores() else cfg["density"]
-        choice = core_select.choose_core(self.rowptr, self.col, self.n, self.m, bar, cfg["step"], cfg["max_side"],
-                                         cfg["max_bytes"], cfg["min_share"])
+        integer = self.row_scale is not None and integer_core_available()
+        if integer:
+            bar, side, cell = cfg["density_int"], cfg["max_side_int"], 2
+        else:
+            bar, side, cell = (cfg["density_tc"] if core_on_tensor_cores() else cfg["density"]), cfg["max_side"], 4
+        choice = core_select.choose_core(self.rowptr, self.col, self.n, self.m, bar, cfg["step"], side,
+                                         cfg["max_bytes"], cfg["min_share"], cell)
+        if choice is None and integer:
+            # nothing worth it at 2 bytes a cell: nothing at 4 either
+            return
         if choice is None:
             return
         dense, rest_rowptr, rest_col, rest_val = core_select.split_core(self.col, self.val, self.n, choice)
+        core_rows, core_cols = choice.rows.int().contiguous(), choice.cols.int().contiguous()
+        if integer:
+            rs, cs = self.row_scale[choice.rows].contiguous(), self.col_scale[choice.cols].contiguous()
+            cnt = core_select.integer_core(dense, rs, cs)
+            if cnt is None:
+                # the values do not factor (scales of another block, weighted edges): choose again under the fp32
+                # rules, which allow less
+                del dense, rest_rowptr, rest_col, rest_val
+                saved, self.row_scale = self.row_scale, None
+                try:
+                    return self.extract_core(depth)
+                finally:
+                    self.row_scale = saved
+            self.core_int = (cnt.to(torch.bfloat16), core_rows, core_cols, rs, cs)
+            del cnt
+            dense = None
         rest = CsrBlock(rest_rowptr, rest_col, rest_val, self.n, self.m)
+        rest.row_scale, rest.col_scale = self.row_scale, self.col_scale
         rest.build_plan(core=False)
         if depth + 1 < int(cfg["rounds"]):
             rest.extract_core(depth + 1)
         self.rest = rest
-        self.core = (dense, choice.rows.int().contiguous(), choice.cols.int().contiguous())
+        self.core = (dense, core_rows, core_cols)
         self.core_split = None
-        if core_on_tensor_cores() and dense.stride(0) % 4 == 0:
+        if dense is not None and core_on_tensor_cores() and dense.stride(0) % 4 == 0:
             hi, lo = torch.empty_like(dense), torch.empty_like(dense)
             with _on(dense.device):
                 _native.check(_native.lib().cagnet_split_tf32_f32(dense.data_ptr(), dense.numel(), hi.data_ptr(),
                                                                   lo.data_ptr(), _stream()), "split_tf32")
             LAUNCHES[0] += 1
             self.core_split = (hi, lo)
+
+    def core_shape(self):
+        """(rows, columns) of the dense core, or None."""
+        if self.core is None:
+            return None
+        m = self.core_int[0] if self.core_int is not None else self.core[0]
+        return int(m.size(0)), int(m.size(1))
+
+    def core_kind(self):
+        """How the dense core is multiplied: "bf16-integer", "3xtf32", "fp32-fma", or None without a core."""
+        if self.core is None:
+            return None
+        if self.core_int is not None:
+            return "bf16-integer"
+        return "3xtf32" if (self.core_split is not None and CORE["tensor_cores"]) else "fp32-fma"
 
     def long_rows(self):
         """Number of rows the plan routes to the block-per-row kernel (synchronises)."""
@@ -283,10 +338,11 @@ def spmm(block, B, C, beta=1.0):
     if B.device != block.val.device or C.device != block.val.device:
         raise RuntimeError("cagnet_b200: spmm operands on different devices")
     f = B.size(1)
-    use_core = block.core is not None and f >= CORE["min_width"] and ldb % 4 == 0 and B.data_ptr() % 16 == 0
+    min_width = CORE["min_width_int"] if block.core_int is not None else CORE["min_width"]
+    use_core = block.core is not None and f >= min_width and ldb % 4 == 0 and B.data_ptr() % 16 == 0
     cores, src = [], block
     while use_core and src.core is not None:
-        cores.append(src.core + (src.core_split,))
+        cores.append(src)
         src = src.rest
     with _on(C.device):
         _native.check(_native.lib().cagnet_spmm_csr_f32(
@@ -294,9 +350,35 @@ def spmm(block, B, C, beta=1.0):
             B.data_ptr(), ldb, C.data_ptr(), ldc, f, float(beta),
             None if src.plan is None else src.plan.data_ptr(), _stream()), "spmm")
         LAUNCHES[0] += 1 if src.plan is None else 2
-        for dense, core_rows, core_cols, split in cores:
-            _core_multiply(dense, core_rows, core_cols, split, B, ldb, C, ldc, f)
+        for owner in cores:
+            if owner.core_int is not None:
+                _core_multiply_int(owner.core_int, B, ldb, C, ldc, f)
+            else:
+                dense, core_rows, core_cols = owner.core
+                _core_multiply(dense, core_rows, core_cols, owner.core_split, B, ldb, C, ldc, f)
     return C
+
+
+def _core_multiply_int(core_int, B, ldb, C, ldc, f):
+    """C[rows] += diag(rs) . (Cnt . (diag(cs) . B[cols])) with Cnt the bf16 multiplicity matrix: the scaled rows of
+    B gathered and cut into three bf16 terms, one tensor-core multiply per k chunk against all three, the sum
+    scaled and added into C's hub rows (current stream, device already current)."""
+    L = _native.lib()
+    cnt, core_rows, core_cols, rs, cs = core_int
+    r, k = cnt.size(0), cnt.size(1)
+    half = (f + 7) // 8 * 8
+    Ys = torch.empty(k * 3 * half, dtype=torch.bfloat16, device=C.device)
+    D = torch.empty(r * 3 * half, dtype=torch.float32, device=C.device)
+    _native.check(L.cagnet_gather_scale_split3_bf16(B.data_ptr(), ldb, core_cols.data_ptr(), cs.data_ptr(), k, f,
+                                                    Ys.data_ptr(), half, _stream()), "gather_scale_split3")
+    nbytes = L.cagnet_core_gemm_int_workspace_bytes(r, k, f)
+    ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=C.device)
+    _native.check(L.cagnet_core_gemm_int_bf16(cnt.data_ptr(), cnt.stride(0), r, k, Ys.data_ptr(), half, D.data_ptr(), f,
+                                              ws.data_ptr(), ws.numel(), _stream()), "core_gemm_int")
+    _native.check(L.cagnet_add_rows_scaled3_f32(D.data_ptr(), half, core_rows.data_ptr(), rs.data_ptr(), r, f,
+                                                C.data_ptr(), ldc, _stream()), "add_rows_scaled3")
+    chunk = _native.get_param("core_chunk")
+    LAUNCHES[0] += 2 + (k + chunk - 1) // chunk
 
 
 def _core_multiply(dense, core_rows, core_cols, split, B, ldb, C, ldc, f):

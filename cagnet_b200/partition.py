@@ -7,7 +7,7 @@ filter and one key sort per block instead of O(P) boolean scans of the whole edg
 on whichever device holds the edge list (the GPU for the large graphs).
 """
 import math
-from typing import NamedTuple
+from typing import NamedTuple, Optional
 
 import torch
 import torch.distributed as dist
@@ -15,12 +15,19 @@ import torch.distributed as dist
 
 
 class Block(NamedTuple):
-    """Coalesced COO block, entries sorted by row then column."""
+    """Coalesced COO block, entries sorted by row then column.
+
+    A normalised block also carries the two diagonal factors it was scaled with: vals[e] =
+    row_scale[rows[e]] * (multiplicity[e] * col_scale[cols[e]]) exactly as computed here (one fp32 rounding per
+    product).  The multiply can use that factorisation: the dense hub-by-hub core of such a block is an integer
+    matrix between two diagonals (see ops.CsrBlock.extract_core)."""
     rows: torch.Tensor   # int64 [nnz]
     cols: torch.Tensor   # int64 [nnz]
     vals: torch.Tensor   # float32 [nnz]
     n_rows: int
     n_cols: int
+    row_scale: Optional[torch.Tensor] = None   # float32 [n_rows]
+    col_scale: Optional[torch.Tensor] = None   # float32 [n_cols]
 
 
 # ------------------------------------------------------------------------------------------ pieces
@@ -68,6 +75,7 @@ def coalesce_block(r, c, n_rows, n_cols, d_row=None, d_col=None):
     vals = counts.to(torch.float32)
     if d_row is not None:
         vals = d_row[rows] * (vals * d_col[cols])
+        return Block(rows, cols, vals, int(n_rows), int(n_cols), d_row.contiguous(), d_col.contiguous())
     return Block(rows, cols, vals, int(n_rows), int(n_cols))
 
 
@@ -85,7 +93,11 @@ def fuse_columns(blocks):
     cols = torch.cat([b.cols + o for b, o in zip(blocks, offs)])
     vals = torch.cat([b.vals for b in blocks])
     order = torch.argsort(rows * offs[-1] + cols)
-    return Block(rows[order], cols[order], vals[order], n_rows, offs[-1])
+    row_scale = col_scale = None
+    if all(b.row_scale is not None and b.col_scale is not None for b in blocks) and \
+            all(b.row_scale is blocks[0].row_scale or torch.equal(b.row_scale, blocks[0].row_scale) for b in blocks):
+        row_scale, col_scale = blocks[0].row_scale, torch.cat([b.col_scale for b in blocks])
+    return Block(rows[order], cols[order], vals[order], n_rows, offs[-1], row_scale, col_scale)
 
 
 def _in_range(x, lo, hi):
@@ -193,7 +205,9 @@ def threed_partition(rank, size, inputs, adj, normalization=False, degree_group=
     s = _in_range(blk.cols, vtx[k], vtx[k + 1])
     # the reference rebuilds the slab from the coalesced indices with unit values (gcn_distr_3d.py:1357-1364)
     vals = blk.vals[s] if normalization else torch.ones_like(blk.vals[s])
-    slab = Block(blk.rows[s], blk.cols[s] - vtx[k], vals, blk.n_rows, vtx[k + 1] - vtx[k])
+    scales = (blk.row_scale, blk.col_scale[vtx[k]:vtx[k + 1]].contiguous()) if (normalization and blk.row_scale is not None) \
+        else (None, None)
+    slab = Block(blk.rows[s], blk.cols[s] - vtx[k], vals, blk.n_rows, vtx[k + 1] - vtx[k], *scales)
     rs = [0]
     for w in chunk_sizes(inputs_2d.size(0), q):
         rs.append(rs[-1] + w)

@@ -62,7 +62,7 @@ def main(argv=None):
         _, blocks = partition.oned_partition(0, 1, torch.zeros(n, 1, device=dev), adj, True)
         del adj
         blk = blocks[0]
-        A = ops.CsrBlock.from_coo(blk.rows, blk.cols, blk.vals, n, n)
+        A = ops.CsrBlock.from_coo(blk.rows, blk.cols, blk.vals, n, n, row_scale=blk.row_scale, col_scale=blk.col_scale)
         del blocks, blk
         torch.cuda.empty_cache()
         cpu_mat, cpu_rate = None, None
@@ -76,9 +76,9 @@ def main(argv=None):
             rec = {"scale": scale, "vertices": n, "nnz": A.nnz, "f": f, "ms": ms, "alg_gbs": alg / ms / 1e6,
                    "frac_of_hbm_peak": alg / ms / 1e6 / peak, "peak_gbs": peak, "peak_source": peak_kind,
                    "gather_gbs": (8 * A.nnz + 4 * A.nnz * f) / ms / 1e6, "hub_rows": A.long_rows(),
-                   "dense_core": None if A.core is None else [int(A.core[0].size(0)), int(A.core[0].size(1)),
-                                                               A.nnz - A.rest.nnz],
-                   "dense_core_used": A.core is not None and f >= ops.CORE["min_width"], "cpu_ms": None,
+                   "dense_core": None if A.core is None else list(A.core_shape()) + [A.nnz - A.rest.nnz, A.core_kind()],
+                   "dense_core_used": A.core is not None and f >= (ops.CORE["min_width_int"] if A.core_int is not None
+                                                                    else ops.CORE["min_width"]), "cpu_ms": None,
                    "cpu_threads": None}
             if cpu_mat is not None:
                 flops = 2.0 * A.nnz * f

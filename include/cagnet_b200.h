@@ -49,7 +49,8 @@ const char* cagnet_last_error_string(void);
  * equal to "spmm_long" by default), "spmm_group_avg" (blocks with at most this many nonzeros per row on average run
  * the lane-group kernel when B is narrower than 128 columns; 0 = never) and "spmm_group_max" (rows up to this length
  * are walked by one lane group there, longer ones by the whole warp; "spmm_group_pool" = consecutive rows per warp,
- * 0 = automatic), "core_chunk" (k length of one tensor-core accumulation of the dense-core
+ * 0 = automatic; "spmm_overlap" = 1 lets the row kernel start under the tail of the hub-row kernel of the same multiply
+ * through a programmatic dependent launch, 0 serialises them), "core_chunk" (k length of one tensor-core accumulation of the dense-core
  * multiply, a multiple of 32).  Host-side global state; returns CAGNET_E_ARG for an unknown name or value. */
 int cagnet_set_param(const char* name, int value);
 int cagnet_get_param(const char* name);
@@ -148,6 +149,29 @@ int cagnet_core_gemm_tc_f32(const float* core_hi, const float* core_lo, int64_t 
                             void* stream);
 int cagnet_add_rows3_f32(const float* D, int64_t half, const int32_t* rows, int32_t R, int32_t f, float* C,
                          int64_t ldc, void* stream);
+
+/* ---- The dense core of a NORMALISED block as an exact integer matrix on the bf16 tensor-core path.  A symmetrically
+ * normalised adjacency value factors as rs[row] * (cnt * cs[col]) with cnt the edge multiplicity
+ * (scale_elements, gcn_distr.py:412-470), so the core is diag(rs) . Cnt . diag(cs) with Cnt small integers, exact in
+ * bf16, and only Y = diag(cs) . B[core_cols] needs splitting (three bf16 terms carry 24 significant bits):
+ *   cagnet_gather_scale_split3_bf16  out[k] = [y1 | y2 | y3] of cs[k] * B[idx[k], 0:f), K rows of 3*half bf16, half >= f
+ *                                    rounded up to a multiple of 8 (columns [f, half) of every part zeroed).
+ *   cagnet_core_gemm_int_bf16        D[R x 3*half] (fp32) = Cnt[R x K] (bf16, ld_cnt) . out, tcgen05 kind::f16 with
+ *                                    fp32 accumulation, the k range cut into "core_chunk" pieces added in fp32.
+ *                                    ws: cagnet_core_gemm_int_workspace_bytes.
+ *   cagnet_add_rows_scaled3_f32      C[rows[i], n] += rs[i] * (D[i, n] + (D[i, half+n] + D[i, 2 half+n])), n < f.
+ * All row starts 16-byte aligned.  cagnet_core_gemm_int_available() is 0 when the library was built without the
+ * CUTLASS header tree; the multiply then returns CAGNET_E_ARG (the two small kernels work regardless).
+ * No counterpart in the reference, which hands normalised values to cuSPARSE like any others
+ * (sparse-extension/sparse_coo_tensor.cu:198-226). */
+int cagnet_core_gemm_int_available(void);
+size_t cagnet_core_gemm_int_workspace_bytes(int32_t R, int32_t K, int32_t f);
+int cagnet_gather_scale_split3_bf16(const float* B, int64_t ldb, const int32_t* idx, const float* cs, int32_t K,
+                                    int32_t f, void* out, int64_t half, void* stream);
+int cagnet_core_gemm_int_bf16(const void* cnt, int64_t ld_cnt, int32_t R, int32_t K, const void* Ys, int64_t half,
+                              float* D, int32_t f, void* ws, size_t ws_bytes, void* stream);
+int cagnet_add_rows_scaled3_f32(const float* D, int64_t half, const int32_t* rows, const float* rs, int32_t R,
+                                int32_t f, float* C, int64_t ldc, void* stream);
 
 /* ---- Z = epilogue(X * W) for a tall X (n x K, ldx) and a small W.
  * transW = 0: W is K x N row-major (ldw);  transW = 1: W is N x K row-major (ldw) and is used

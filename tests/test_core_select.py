@@ -89,3 +89,25 @@ def test_rectangular_block_of_a_block_row():
     full[ch.rows[:, None], ch.cols[None, :]] += dense
     want = torch.sparse_coo_tensor(torch.stack([rows, cols]), vals, (hi - lo, n)).to_dense()
     assert torch.equal(full, want)
+
+
+def test_integer_core_recovers_multiplicities_exactly():
+    """dense = fl32(rs * fl32(cnt * cs)) factors back into the integer matrix; anything else is refused."""
+    g = torch.Generator().manual_seed(11)
+    r, c = 96, 160
+    cnt = (torch.rand(r, c, generator=g) < 0.3).float()
+    cnt[3, 5], cnt[7, 7] = 2.0, 3.0
+    rs = torch.rand(r, generator=g).double().pow(-0.5).float()
+    cs = torch.rand(c, generator=g).double().pow(-0.5).float()
+    cs[9] = 0.0                                                     # a padding column: no entry refers to it
+    cnt[:, 9] = 0.0
+    dense = rs[:, None] * (cnt * cs[None, :])
+    got = core_select.integer_core(dense, rs, cs)
+    assert got is not None and torch.equal(got, cnt)
+    assert torch.equal(got.bfloat16().float(), cnt)                 # small integers are exact in bf16
+    assert core_select.integer_core(dense, rs * 1.0001, cs) is None
+    weighted = dense.clone()
+    weighted[0, 0] = 0.123
+    assert core_select.integer_core(weighted, rs, cs) is None
+    big = rs[:, None] * (cnt * 300 * cs[None, :])
+    assert core_select.integer_core(big, rs, cs) is None            # multiplicity beyond what bf16 holds exactly

@@ -490,6 +490,92 @@ def _spmm_with_core(blk, n, f, beta):
     _close(Cn, torch.sparse.mm(_dense64(blk), Bn.double()))
 
 
+@pytest.mark.parametrize("f,beta", [(602, 0.0), (130, 1.0), (128, 0.0), (41, 1.0), (16, 0.0)])
+def test_spmm_with_integer_core_matches_oracle(f, beta):
+    """A normalised block that carries its diagonal factors keeps its core as bf16 edge multiplicities and multiplies
+    it with three bf16 tensor-core products: same product as the fp64 oracle, to the same tolerance."""
+    if not ops.integer_core_available():
+        pytest.skip("library built without the tensor-core kernels")
+    n = 4096
+    edge = graphs.rmat_graph(n, target_nnz=n * 96, seed=5)
+    adj = graphs.add_self_loops(edge, n)
+    _, blocks = PP.oned_partition(0, 1, torch.zeros(n, 1), adj, True)
+    blk = blocks[0]
+    assert blk.row_scale is not None and blk.col_scale is not None
+    old = ops.configure_core(enabled=True, step=64, max_side_int=2048, min_share=0.0, density_int=0.05, min_width_int=16)
+    try:
+        A = ops.CsrBlock.from_coo(blk.rows, blk.cols, blk.vals, n, n, row_scale=blk.row_scale, col_scale=blk.col_scale)
+        assert A.core_kind() == "bf16-integer"
+        cnt = A.core_int[0]
+        assert int((cnt != 0).sum()) + A.rest.nnz == A.nnz and float(cnt.float().max()) == 1.0
+        g = torch.Generator().manual_seed(f)
+        B, C0 = torch.randn(n, f, generator=g), torch.randn(n, f, generator=g)
+        want = beta * C0.double() + torch.sparse.mm(_dense64(blk), B.double())
+        C = _poison_pads(ops.to_padded(C0.cuda()))
+        before = ops.launch_count()
+        ops.spmm(A, _poison_pads(ops.to_padded(B.cuda())), C, beta)
+        assert ops.launch_count() - before > 2                      # the core kernels ran
+        _close(C, want)
+        # scales that do not belong to the block: the values do not factor, the fp32 core is kept
+        wrong = ops.CsrBlock.from_coo(blk.rows, blk.cols, blk.vals, n, n, row_scale=blk.row_scale * 1.5,
+                                      col_scale=blk.col_scale)
+        assert wrong.core_int is None
+        # an edge listed twice has multiplicity 2: still an exact small integer
+        dup = torch.cat([adj, adj[:, :5000]], dim=1)
+        _, blocks2 = PP.oned_partition(0, 1, torch.zeros(n, 1), dup, True)
+        b2 = blocks2[0]
+        A2 = ops.CsrBlock.from_coo(b2.rows, b2.cols, b2.vals, n, n, row_scale=b2.row_scale, col_scale=b2.col_scale)
+        if A2.core_int is not None:
+            C2 = ops.zeros_padded(n, f, "cuda")
+            ops.spmm(A2, ops.to_padded(B.cuda()), C2, 0.0)
+            _close(C2, torch.sparse.mm(_dense64(b2), B.double()))
+    finally:
+        ops.configure_core(**old)
+
+
+def test_integer_core_kernels_through_the_c_abi():
+    """gather + scale + three-term bf16 split, the chunked bf16 multiply and the scaled row add, one by one."""
+    if _native.lib().cagnet_core_gemm_int_available() != 1:
+        pytest.skip("library built without the tensor-core kernels")
+    L = _native.lib()
+    g = torch.Generator().manual_seed(3)
+    m, f, K, R = 900, 130, 384, 256
+    B = ops.to_padded(torch.randn(m, f, generator=g).cuda())
+    idx = torch.randperm(m, generator=g)[:K].int().cuda()
+    cs = torch.rand(K, generator=g).cuda() + 0.1
+    half = (f + 7) // 8 * 8
+    Ys = torch.full((K, 3 * half), float("nan"), dtype=torch.bfloat16, device="cuda")
+    _native.check(L.cagnet_gather_scale_split3_bf16(B.data_ptr(), B.stride(0), idx.data_ptr(), cs.data_ptr(), K, f,
+                                                    Ys.data_ptr(), half, None), "gather_scale_split3")
+    y = cs[:, None] * B[idx.long()]
+    parts = Ys.view(K, 3, half).float()
+    assert torch.equal(parts[:, 0, :f], y.bfloat16().float())
+    total = parts[:, 0, :f].double() + parts[:, 1, :f].double() + parts[:, 2, :f].double()
+    assert float((total - y.double()).abs().max()) <= 2.0 ** -23 * float(y.abs().max())
+    assert float(parts[:, :, f:].abs().max()) == 0.0                       # pad columns are zeros, not NaN
+    cnt = (torch.rand(R, K, generator=g) < 0.2).to(torch.bfloat16).cuda()
+    cnt[0, :7] = 2.0
+    D = torch.empty(R, 3 * half, device="cuda")
+    ws = torch.empty(max(L.cagnet_core_gemm_int_workspace_bytes(R, K, f), 16), dtype=torch.uint8, device="cuda")
+    old_chunk = _native.get_param("core_chunk")
+    try:
+        _native.set_param("core_chunk", 256)                               # two k chunks
+        _native.check(L.cagnet_core_gemm_int_bf16(cnt.data_ptr(), K, R, K, Ys.data_ptr(), half, D.data_ptr(), f,
+                                                  ws.data_ptr(), ws.numel(), None), "core_gemm_int")
+    finally:
+        _native.set_param("core_chunk", old_chunk)
+    _close(D, cnt.double().cpu() @ Ys.double().cpu(), rel=1e-5)
+    rows = torch.randperm(700, generator=g)[:R].int().cuda()
+    rs = torch.rand(R, generator=g).cuda() + 0.1
+    C0 = torch.randn(700, f, generator=g)
+    C = _poison_pads(ops.to_padded(C0.cuda()))
+    _native.check(L.cagnet_add_rows_scaled3_f32(D.data_ptr(), half, rows.data_ptr(), rs.data_ptr(), R, f, C.data_ptr(),
+                                                C.stride(0), None), "add_rows_scaled3")
+    want = C0.double()
+    want[rows.long().cpu()] += (rs.double()[:, None] * (cnt.double() @ y.double())).cpu()
+    _close(C, want)
+
+
 def test_no_core_for_uniform_graphs():
     blk = _random_block(5000, 5000, 20, seed=3)
     old = ops.configure_core(step=256, max_side=2048)
