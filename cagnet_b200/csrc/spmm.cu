@@ -32,6 +32,7 @@ struct Tuning {
   int spmm_group_avg = 96;      // blocks with at most this many nonzeros per row on average use it (0 = never)
   int spmm_group_pool = 0;      // rows per warp pool there: 0 = automatic, else 4, 8, 16 or 32
   int spmm_overlap = 1;         // the row kernel may start under the hub-row kernel's tail (programmatic launch)
+  int spmm_deep = 1;            // narrow B: gathers issued in batches of 4-8 per lane before their FMAs
 };
 static Tuning g_tuning;
 
@@ -39,6 +40,7 @@ constexpr int kPlanMagic = 0x0CA67E70;
 constexpr int kPlanHeaderInts = 8;   // [0] magic [1] count [2] threshold [3] capacity
 constexpr int kMinLongThreshold = 256;
 constexpr int kLongWarps = 16;
+constexpr int kStagePairs = 64;    // (col, val) pairs a warp parks in shared memory at a time
 
 // ------------------------------------------------------------------------------------------------
 template <int VEC>
@@ -117,10 +119,94 @@ __device__ __forceinline__ void pdl_wait_for_primary() { asm volatile("griddepco
 // 128-bit gather and the FMAs -- the first version handed the pairs round with two warp shuffles per nonzero
 // and a 64-bit multiply, 22 instructions per nonzero, and ran at half of the issue rate without saturating
 // either L2 or HBM.
+//
+// Narrow B (LPN < 32, several lane groups per warp) is bound by memory latency, not bandwidth: a gathered row is
+// 64-256 bytes and nothing else keeps the warp busy while it travels.  There the pairs of a chunk are consumed in
+// batches: the batch's pairs are read from shared memory, then ALL its gathers are issued into registers, and only
+// then do the FMAs run (in nonzero order, so the sums are the same numbers as one gather at a time would give).
+// A lane then has 4-8 independent 128-bit gathers in flight instead of whatever the compiler chose to overlap; with
+// 4 lanes per nonzero a chunk is 64 pairs, so that a batch of 8 exists.
 template <int VEC, int LPN, int NV>
+__device__ __forceinline__ void accumulate_range_batched(const int* __restrict__ col, const float* __restrict__ val,
+                                                         int start, int end, const float* __restrict__ bt, int ldb,
+                                                         int nvalid, int lane, int2* stage, float (&acc)[NV][VEC]) {
+  static_assert(LPN < 32, "batched gathers are for narrow B");
+  constexpr int G = 32 / LPN;
+  constexpr int CH = (LPN <= 4) ? 64 : 32;         // pairs staged per chunk
+  constexpr int PER = CH / G;                      // pairs one lane group consumes per chunk
+  constexpr int BATCH = (NV >= 2) ? 4 : 8;         // gathers in flight per lane
+  static_assert(PER % BATCH == 0 && CH <= kStagePairs, "chunk / batch mismatch");
+  const int sub = lane / LPN;
+  auto load_pair = [&](int e) {
+    int2 p = make_int2(0, 0);
+    if (e < end) {
+      p.x = __ldg(col + e);
+      p.y = __float_as_int(__ldg(val + e));
+    }
+    return p;
+  };
+  int2 next0 = load_pair(start + lane), next1 = make_int2(0, 0);
+  if constexpr (CH == 64) next1 = load_pair(start + 32 + lane);
+  for (int base = start; base < end; base += CH) {
+    __syncwarp();            // every lane is done with the previous chunk
+    stage[lane] = next0;
+    if constexpr (CH == 64) stage[32 + lane] = next1;
+    __syncwarp();
+    next0 = load_pair(base + CH + lane);           // the following chunk's pairs travel while this one is gathered
+    if constexpr (CH == 64) next1 = load_pair(base + CH + 32 + lane);
+    const int cnt = min(CH, end - base);
+#pragma unroll
+    for (int b = 0; b < PER; b += BATCH) {
+      if (b * G >= cnt) break;                     // warp-uniform
+      int c[BATCH];
+      float v[BATCH];
+#pragma unroll
+      for (int i = 0; i < BATCH; ++i) {
+        const int idx = (b + i) * G + sub;
+        const int2 q = stage[min(idx, CH - 1)];
+        c[i] = idx < cnt ? q.x : -1;
+        v[i] = idx < cnt ? __int_as_float(q.y) : 0.f;
+      }
+      float x[BATCH][NV][VEC];
+#pragma unroll
+      for (int i = 0; i < BATCH; ++i) {
+        const float* bp = bt + static_cast<int64_t>(c[i] < 0 ? 0 : c[i]) * ldb;
+#pragma unroll
+        for (int k = 0; k < NV; ++k) {
+          if (c[i] >= 0 && k < nvalid) {
+            load_vec<VEC>(bp + k * (LPN * VEC), x[i][k]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < VEC; ++j) x[i][k][j] = 0.f;
+          }
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < BATCH; ++i)
+#pragma unroll
+        for (int k = 0; k < NV; ++k)
+#pragma unroll
+          for (int j = 0; j < VEC; ++j) acc[k][j] = fmaf(v[i], x[i][k][j], acc[k][j]);
+    }
+  }
+  // fold the 32/LPN nonzero slots of the warp together; afterwards every lane holds the row sums
+#pragma unroll
+  for (int off = LPN; off < 32; off <<= 1) {
+#pragma unroll
+    for (int k = 0; k < NV; ++k)
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) acc[k][j] += __shfl_xor_sync(0xffffffffu, acc[k][j], off);
+  }
+}
+
+template <int VEC, int LPN, int NV, bool DEEP = false>
 __device__ __forceinline__ void accumulate_range(const int* __restrict__ col, const float* __restrict__ val,
                                                  int start, int end, const float* __restrict__ bt, int ldb,
                                                  int nvalid, int lane, int2* stage, float (&acc)[NV][VEC]) {
+  if constexpr (DEEP && LPN < 32) {
+    accumulate_range_batched<VEC, LPN, NV>(col, val, start, end, bt, ldb, nvalid, lane, stage, acc);
+    return;
+  }
   constexpr int G = 32 / LPN;                      // nonzeros in flight per warp step
 #ifndef CAGNET_SPMM_UNROLL
 #define CAGNET_SPMM_UNROLL 8
@@ -200,12 +286,12 @@ __device__ __forceinline__ int live_vectors(int tile0, int l, int f_eff) {
 
 constexpr int kMaxRowsPerBlock = 8;
 
-template <int VEC, int LPN, int NV>
+template <int VEC, int LPN, int NV, bool DEEP>
 __global__ void __launch_bounds__(kMaxRowsPerBlock * 32) spmm_warp_rows_kernel(
     const int* __restrict__ rowptr, const int* __restrict__ col, const float* __restrict__ val, int n,
     const float* __restrict__ B, int ldb, float* __restrict__ C, int ldc, int f_eff, int f, float beta,
     const int* __restrict__ plan, int min_threshold) {
-  __shared__ __align__(16) int2 stage[kMaxRowsPerBlock][32];
+  __shared__ __align__(16) int2 stage[kMaxRowsPerBlock][kStagePairs];
   const int warp = threadIdx.x >> 5;
   const int row = blockIdx.x * (blockDim.x >> 5) + warp;
   if (row >= n) return;                      // whole warps leave together; nothing below is block-wide
@@ -227,7 +313,7 @@ __global__ void __launch_bounds__(kMaxRowsPerBlock * 32) spmm_warp_rows_kernel(
 #pragma unroll
     for (int j = 0; j < VEC; ++j) acc[k][j] = 0.f;
 
-  accumulate_range<VEC, LPN, NV>(col, val, start, end, B + tile0 + l * VEC, ldb, nvalid, lane, stage[warp], acc);
+  accumulate_range<VEC, LPN, NV, DEEP>(col, val, start, end, B + tile0 + l * VEC, ldb, nvalid, lane, stage[warp], acc);
 
   if (lane < LPN)
     store_row<VEC, LPN, NV>(C + static_cast<int64_t>(row) * ldc + tile0 + l * VEC, tile0 + l * VEC, f, nvalid, beta, acc);
@@ -248,15 +334,18 @@ __global__ void __launch_bounds__(kMaxRowsPerBlock * 32) spmm_warp_rows_kernel(
 //   hub     rows are skipped: the block-per-row kernel owns them.
 // Per short row this costs a few instructions of bookkeeping instead of a warp's offsets load, stage, two
 // warp barriers and a shuffle tree.
-template <int VEC, int LPN, int NV>
+template <int VEC, int LPN, int NV, bool DEEP>
 __global__ void __launch_bounds__(kMaxRowsPerBlock * 32) spmm_group_rows_kernel(
     const int* __restrict__ rowptr, const int* __restrict__ col, const float* __restrict__ val, int n,
     const float* __restrict__ B, int ldb, float* __restrict__ C, int ldc, int f_eff, int f, float beta,
     const int* __restrict__ plan, int min_threshold, int group_max, int pool) {
   static_assert(LPN < 32, "the lane-group kernel needs at least two groups per warp");
   constexpr int G = 32 / LPN;
-  constexpr int UNROLL = (NV >= 2) ? 4 : 8;
-  __shared__ __align__(16) int2 stage[kMaxRowsPerBlock][32];
+#ifndef CAGNET_GROUP_UNROLL
+#define CAGNET_GROUP_UNROLL 8
+#endif
+  constexpr int UNROLL = (NV >= 2) ? CAGNET_GROUP_UNROLL / 2 : CAGNET_GROUP_UNROLL;
+  __shared__ __align__(16) int2 stage[kMaxRowsPerBlock][kStagePairs];
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int row0 = (blockIdx.x * (blockDim.x >> 5) + warp) * pool;
@@ -354,21 +443,21 @@ __global__ void __launch_bounds__(kMaxRowsPerBlock * 32) spmm_group_rows_kernel(
     for (int k = 0; k < NV; ++k)
 #pragma unroll
       for (int j = 0; j < VEC; ++j) acc[k][j] = 0.f;
-    accumulate_range<VEC, LPN, NV>(col, val, start, end, bt, ldb, nvalid, lane, stage[warp], acc);
+    accumulate_range<VEC, LPN, NV, DEEP>(col, val, start, end, bt, ldb, nvalid, lane, stage[warp], acc);
     if (lane < LPN)
       store_row<VEC, LPN, NV>(C + static_cast<int64_t>(row0 + i) * ldc + column0, column0, f, nvalid, beta, acc);
   }
   pdl_wait_for_primary();
 }
 
-template <int VEC, int LPN, int NV>
+template <int VEC, int LPN, int NV, bool DEEP>
 __global__ void __launch_bounds__(kLongWarps * 32) spmm_block_rows_kernel(
     const int* __restrict__ rowptr, const int* __restrict__ col, const float* __restrict__ val,
     const float* __restrict__ B, int ldb, float* __restrict__ C, int ldc, int f_eff, int f, float beta,
     const int* __restrict__ plan, int min_threshold) {
   constexpr int TILE = LPN * VEC * NV;
   __shared__ float part[kLongWarps][TILE];
-  __shared__ __align__(16) int2 stage[kLongWarps][32];
+  __shared__ __align__(16) int2 stage[kLongWarps][kStagePairs];
   pdl_release_dependents();
   const int long_threshold = max(__ldg(plan + 2), min_threshold);
   const int count = min(__ldg(plan + 1), __ldg(plan + 3));
@@ -384,7 +473,7 @@ __global__ void __launch_bounds__(kLongWarps * 32) spmm_block_rows_kernel(
     const int start = __ldg(rowptr + row);
     const int end = __ldg(rowptr + row + 1);
     if (end - start <= long_threshold) continue;   // listed, but short enough for the warp-per-row pass at this width
-    const int per = (((end - start) + kLongWarps - 1) / kLongWarps + 31) & ~31;
+    const int per = (((end - start) + kLongWarps - 1) / kLongWarps + kStagePairs - 1) & ~(kStagePairs - 1);
     const int ws = min(end, start + warp * per);
     const int we = min(end, ws + per);
 
@@ -393,7 +482,7 @@ __global__ void __launch_bounds__(kLongWarps * 32) spmm_block_rows_kernel(
     for (int k = 0; k < NV; ++k)
 #pragma unroll
       for (int j = 0; j < VEC; ++j) acc[k][j] = 0.f;
-    accumulate_range<VEC, LPN, NV>(col, val, ws, we, B + tile0 + l * VEC, ldb, nvalid, lane, stage[warp], acc);
+    accumulate_range<VEC, LPN, NV, DEEP>(col, val, ws, we, B + tile0 + l * VEC, ldb, nvalid, lane, stage[warp], acc);
 
     if (lane < LPN) {
 #pragma unroll
@@ -459,8 +548,8 @@ static int group_pool_rows(int n) {
   return pool;
 }
 
-template <int VEC, int LPN, int NV>
-static int launch_spmm(const int* rowptr, const int* col, const float* val, int n, int m, int64_t nnz, const float* B,
+template <int VEC, int LPN, int NV, bool DEEP>
+static int launch_spmm_impl(const int* rowptr, const int* col, const float* val, int n, int m, int64_t nnz, const float* B,
                        int64_t ldb64, float* C, int64_t ldc64, int f_eff, int f, float beta, const int* plan,
                        cudaStream_t stream) {
   const int ldb = static_cast<int>(ldb64), ldc = static_cast<int>(ldc64);   // checked to fit by the entry point
@@ -472,7 +561,7 @@ static int launch_spmm(const int* rowptr, const int* col, const float* val, int 
     // grid-stride over the listed rows, so any grid size is correct; this one is tight for the
     // current threshold and never below one wave
     const int blocks = max(1, min(plan_capacity(nnz, max(g_tuning.spmm_long, kMinLongThreshold)), 16 * kNumSMs));
-    spmm_block_rows_kernel<VEC, LPN, NV><<<dim3(blocks, tiles), kLongWarps * 32, 0, stream>>>(
+    spmm_block_rows_kernel<VEC, LPN, NV, DEEP><<<dim3(blocks, tiles), kLongWarps * 32, 0, stream>>>(
         rowptr, col, val, B, ldb, C, ldc, f_eff, f, beta, plan, min_threshold);
   }
   const int rows_per_block = g_tuning.spmm_rpb;
@@ -494,13 +583,13 @@ static int launch_spmm(const int* rowptr, const int* col, const float* val, int 
       const int pool = group_pool_rows(n);
       const int pools = (n + pool - 1) / pool;
       cfg.gridDim = dim3((pools + rows_per_block - 1) / rows_per_block, tiles);
-      e = cudaLaunchKernelEx(&cfg, spmm_group_rows_kernel<VEC, LPN, NV>, rowptr, col, val, n, B, ldb, C, ldc, f_eff, f,
+      e = cudaLaunchKernelEx(&cfg, spmm_group_rows_kernel<VEC, LPN, NV, DEEP>, rowptr, col, val, n, B, ldb, C, ldc, f_eff, f,
                              beta, plan, min_threshold, g_tuning.spmm_group_max, pool);
     }
   }
   if (!grouped) {
     cfg.gridDim = dim3((n + rows_per_block - 1) / rows_per_block, tiles);
-    e = cudaLaunchKernelEx(&cfg, spmm_warp_rows_kernel<VEC, LPN, NV>, rowptr, col, val, n, B, ldb, C, ldc, f_eff, f, beta,
+    e = cudaLaunchKernelEx(&cfg, spmm_warp_rows_kernel<VEC, LPN, NV, DEEP>, rowptr, col, val, n, B, ldb, C, ldc, f_eff, f, beta,
                            plan, min_threshold);
   }
   if (e != cudaSuccess) {
@@ -509,6 +598,22 @@ static int launch_spmm(const int* rowptr, const int* col, const float* val, int 
     return CAGNET_E_LAUNCH;
   }
   return check_launch("cagnet_spmm_csr_f32");
+}
+
+template <int VEC, int LPN, int NV>
+static int launch_spmm(const int* rowptr, const int* col, const float* val, int n, int m, int64_t nnz, const float* B,
+                       int64_t ldb64, float* C, int64_t ldc64, int f_eff, int f, float beta, const int* plan,
+                       cudaStream_t stream) {
+  // Batched gathers pay where the multiply waits on memory latency with little else to run: one vector per lane
+  // (at most 16 columns) on a block of short rows.  Measured on R-MAT graphs with 31 nonzeros per row: width 16
+  // 0.585 -> 0.432 ms (1 M vertices), 2.09 -> 1.55 ms (4 M); but width 64 (two vectors per lane) 1.19 -> 1.30 ms, and
+  // on a 233K-vertex graph with 493 nonzeros per row, where enough warps are resident to hide the latency and the
+  // extra registers cost occupancy, width 16 0.80 -> 1.04 ms and width 41 1.62 -> 2.37 ms.
+  if constexpr (LPN < 32 && NV == 1) {
+    if (g_tuning.spmm_deep && g_tuning.spmm_group_avg > 0 && nnz <= static_cast<int64_t>(g_tuning.spmm_group_avg) * n)
+      return launch_spmm_impl<VEC, LPN, NV, true>(rowptr, col, val, n, m, nnz, B, ldb64, C, ldc64, f_eff, f, beta, plan, stream);
+  }
+  return launch_spmm_impl<VEC, LPN, NV, false>(rowptr, col, val, n, m, nnz, B, ldb64, C, ldc64, f_eff, f, beta, plan, stream);
 }
 
 // Feature tiling.  A tile is `tile` vectors wide (tile * VEC columns); narrow B is covered by one tile of the
@@ -576,6 +681,10 @@ extern "C" int cagnet_set_param(const char* name, int value) {
     if (set_core_chunk(value)) return fail(CAGNET_E_ARG, "cagnet_set_param: core_chunk must be a multiple of 32, >= 256");
     return CAGNET_OK;
   }
+  if (!strcmp(name, "core_tile")) {
+    if (set_core_tile(value)) return fail(CAGNET_E_ARG, "cagnet_set_param: core_tile must be 0 or 1 (and needs the tensor-core build)");
+    return CAGNET_OK;
+  }
   if (!strcmp(name, "spmm_long_narrow")) {
     if (value < kMinLongThreshold) return fail(CAGNET_E_ARG, "cagnet_set_param: spmm_long_narrow must be >= 256");
     g_tuning.spmm_long_narrow = value;
@@ -590,6 +699,10 @@ extern "C" int cagnet_set_param(const char* name, int value) {
     if (value != 0 && value != 4 && value != 8 && value != 16 && value != 32)
       return fail(CAGNET_E_ARG, "cagnet_set_param: spmm_group_pool must be 0, 4, 8, 16 or 32");
     g_tuning.spmm_group_pool = value;
+    return CAGNET_OK;
+  }
+  if (!strcmp(name, "spmm_deep")) {
+    g_tuning.spmm_deep = value != 0;
     return CAGNET_OK;
   }
   if (!strcmp(name, "spmm_overlap")) {
@@ -618,7 +731,9 @@ extern "C" int cagnet_get_param(const char* name) {
   if (name && !strcmp(name, "spmm_group_avg")) return g_tuning.spmm_group_avg;
   if (name && !strcmp(name, "spmm_group_pool")) return g_tuning.spmm_group_pool;
   if (name && !strcmp(name, "spmm_overlap")) return g_tuning.spmm_overlap;
+  if (name && !strcmp(name, "spmm_deep")) return g_tuning.spmm_deep;
   if (name && !strcmp(name, "core_chunk")) return core_chunk();
+  if (name && !strcmp(name, "core_tile")) return core_tile();
   return -1;
 }
 

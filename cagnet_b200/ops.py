@@ -147,7 +147,7 @@ def _row_major(t):
 CORE = {"enabled": os.environ.get("CAGNET_DENSE_CORE", "1") != "0", "density": 0.2, "density_tc": 0.09, "step": 1024,
         "max_side": 16384, "max_bytes": 2 << 30, "min_share": 0.1, "min_width": 128, "rounds": 1,
         "tensor_cores": os.environ.get("CAGNET_CORE_TENSOR", "1") != "0",
-        "integer": os.environ.get("CAGNET_CORE_INTEGER", "1") != "0", "density_int": 0.03, "max_side_int": 32768,
+        "integer": os.environ.get("CAGNET_CORE_INTEGER", "1") != "0", "density_int": 0.02, "max_side_int": 32768,
         "min_width_int": 128}
 
 

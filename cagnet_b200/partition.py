@@ -115,11 +115,14 @@ def oned_partition(rank, size, inputs, adj, normalization=True, replication=1, d
     vtx = boundaries(n, n_per_proc)
     lo, hi = vtx[rank_c], vtx[rank_c + 1]
     d = inv_sqrt_degree(adj, n, degree_group) if normalization else None
-    sel = _in_range(adj[1], lo, hi)
-    u, v = adj[0][sel], adj[1][sel] - lo
+    if lo == 0 and hi == n:
+        u, v = adj[0], adj[1]                 # one block row: nothing to filter (and no 2 x E copy at 1.3 G edges)
+    else:
+        sel = _in_range(adj[1], lo, hi)
+        u, v = adj[0][sel], adj[1][sel] - lo
     blocks = []
     for i in range(len(vtx) - 1):
-        s = _in_range(u, vtx[i], vtx[i + 1])
+        s = slice(None) if len(vtx) == 2 else _in_range(u, vtx[i], vtx[i + 1])
         n_i = vtx[i + 1] - vtx[i]
         # stored orientation: row = column vertex of A (local to this rank), column = row vertex (local to block i)
         if normalization:
