@@ -33,8 +33,6 @@ constexpr int kNumSMs = 148;  // B200
 // k length of one tensor-core accumulation of the dense-core multiply (tuning knob "core_chunk")
 int core_chunk();
 int set_core_chunk(int value);
-// tiling of the integer-core multiply (tuning knob "core_tile"): 0 = one SM per tile, 1 = SM pairs
-int core_tile();
-int set_core_tile(int value);
+
 
 }  // namespace cagnet

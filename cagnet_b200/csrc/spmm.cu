@@ -681,10 +681,6 @@ extern "C" int cagnet_set_param(const char* name, int value) {
     if (set_core_chunk(value)) return fail(CAGNET_E_ARG, "cagnet_set_param: core_chunk must be a multiple of 32, >= 256");
     return CAGNET_OK;
   }
-  if (!strcmp(name, "core_tile")) {
-    if (set_core_tile(value)) return fail(CAGNET_E_ARG, "cagnet_set_param: core_tile must be 0 or 1 (and needs the tensor-core build)");
-    return CAGNET_OK;
-  }
   if (!strcmp(name, "spmm_long_narrow")) {
     if (value < kMinLongThreshold) return fail(CAGNET_E_ARG, "cagnet_set_param: spmm_long_narrow must be >= 256");
     g_tuning.spmm_long_narrow = value;
@@ -733,7 +729,6 @@ extern "C" int cagnet_get_param(const char* name) {
   if (name && !strcmp(name, "spmm_overlap")) return g_tuning.spmm_overlap;
   if (name && !strcmp(name, "spmm_deep")) return g_tuning.spmm_deep;
   if (name && !strcmp(name, "core_chunk")) return core_chunk();
-  if (name && !strcmp(name, "core_tile")) return core_tile();
   return -1;
 }
 

@@ -107,3 +107,28 @@ def test_1d_two_gpus_against_oracle(golden_dir):
             np.testing.assert_allclose(res[f"ep{ep}_out"], rec[ep]["out"][rows].numpy(), rtol=1e-4, atol=2e-5)
             np.testing.assert_allclose(res[f"ep{ep}_gw1"], rec[ep]["gW1"].numpy(), rtol=1e-4, atol=2e-5)
             np.testing.assert_allclose(res[f"ep{ep}_w1"], rec[ep]["W1"].numpy(), rtol=1e-4, atol=2e-5)
+
+
+def _oracle_worker(rank, world, algo, replication):
+    """One epoch of the benchmark's parity graph through the CUDA kernels and NCCL; rank 0 returns the errors
+    against the fp64 oracle at the same rank count (what `bench.py` prints as "parity")."""
+    import argparse
+    import torch
+    import bench
+    args = argparse.Namespace(replication=replication, order="reference", stage_groups=-1, collective="all_gather",
+                              prefetch=1, cache_blocks=1)
+    ctx = bench.Context(rank, world, torch.device("cuda", rank))
+    result, ok = bench.parity_leg(ctx, algo, args)
+    return result
+
+
+@pytest.mark.parametrize("algo,world,c", [("1d", 2, 1), ("1d", 4, 1), ("15d", 4, 2), ("2d", 4, 1), ("1d", 8, 1),
+                                          ("15d", 8, 2), ("3d", 8, 1)])
+def test_epoch_against_oracle_at_the_same_rank_count(algo, world, c):
+    """Every schedule at P = 2, 4 or 8 on a 4,099-vertex R-MAT graph (normalised, activated, partial train mask, rows
+    not divisible by P): rank-local outputs, loss and weight gradients against the oracle evaluated for that P."""
+    if _gpus() < world:
+        pytest.skip(f"needs {world} GPUs")
+    res = run_ranks(world, _oracle_worker, algo, c, backend="nccl", timeout=600)[0]
+    assert res["ok"], res
+    assert res["out"] <= 1e-4 and res["loss"] <= 1e-4 and res["gW1"] <= 1e-3 and res["gW2"] <= 1e-3
