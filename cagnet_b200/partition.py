@@ -55,7 +55,8 @@ def inv_sqrt_degree(adj, node_count, group=None):
     call) every member counts its own 1/P slice of the list and one all-reduce of the int64 counts gives the
     degrees: the same integers as the reference's count over the whole list on every rank, at 1/P of the scan."""
     rows = adj[0]
-    if group is not None and dist.is_initialized() and dist.get_world_size(group) > 1:
+    if group is not None and dist.is_initialized() and dist.get_world_size(group) > 1 and \
+            rows.is_cuda == (dist.get_backend(group) == "nccl"):      # NCCL reduces device tensors only, Gloo host ones
         size, rank = dist.get_world_size(group), dist.get_rank(group)
         per = -(-rows.numel() // size)
         deg = torch.bincount(rows[rank * per:(rank + 1) * per], minlength=node_count)
