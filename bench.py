@@ -68,7 +68,7 @@ def dense_core_info(model):
     """What rank 0's first adjacency block was split into (rows x columns of the dense core, its nonzeros, and
     whether it is multiplied on the tensor cores), or None when the block is all-sparse."""
     try:
-        blk = model.am_pbyp.groups[0].block
+        blk = model.am_pbyp.groups[0].block if hasattr(model, "am_pbyp") else model.adj_block
         if blk.core is None:
             return None
         rows, cols = blk.core_shape()

@@ -103,11 +103,15 @@ __device__ __forceinline__ void store_row(float* __restrict__ cp, int column0, i
 // The hub-row kernel and the row kernel of one multiply write disjoint rows of C, so they may overlap: the hub
 // kernel's longest row (100K+ nonzeros in an R-MAT graph, one thread block) would otherwise be a tail during which
 // the rest of the GPU idles.  The row kernel is launched with programmatic stream serialisation: it may start as
-// soon as every block of the hub kernel has begun (`pdl_release_dependents`), and each of its threads waits for
-// the hub kernel to have completed before it exits (`pdl_wait_for_primary`), so that whatever follows in the stream
-// still sees both kernels finished.  Without a preceding hub kernel both are no-ops.
+// soon as every block of the hub kernel has begun (`pdl_release_dependents`), and it does not complete before the
+// hub kernel has (`pdl_wait_for_primary`, executed before a thread exits), so that whatever follows in the stream
+// still sees both kernels finished.  Only the row kernel's FIRST block waits: a grid is complete when all its blocks
+// are, so one waiting block is enough to order the completions, and the other blocks leave at once instead of
+// holding their SM slots until the hub kernel's last row is done.  Without a preceding hub kernel both are no-ops.
 __device__ __forceinline__ void pdl_release_dependents() { asm volatile("griddepcontrol.launch_dependents;"); }
-__device__ __forceinline__ void pdl_wait_for_primary() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait_for_primary() {
+  if (blockIdx.x == 0 && blockIdx.y == 0) asm volatile("griddepcontrol.wait;" ::: "memory");
+}
 
 // Accumulates sum_e val[e] * B[col[e], tile columns of this lane] over e in [start, end) into acc.
 // bt already points at column (tile0 + l*VEC) of row 0 of B; vector k of the lane sits k*LPN*VEC columns

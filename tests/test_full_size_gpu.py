@@ -37,6 +37,17 @@ def test_benchmark_graph_checksum_linearity_and_core_agreement():
     ops.spmm(A, b1, c1, 0.0)
     ops.spmm(plain, b1, cp, 0.0)
     assert _rel(c1, cp) <= 1e-5                     # same product with and without the dense core
+    if ops.integer_core_available():
+        # the block with its normalisation factors: the core becomes bf16 edge multiplicities between two diagonals
+        Ai = ops.CsrBlock.from_coo(blk.rows, blk.cols, blk.vals, n, n, row_scale=blk.row_scale, col_scale=blk.col_scale)
+        assert Ai.core_kind() == "bf16-integer"
+        cnt = Ai.core_int[0]
+        assert Ai.rest.nnz + int((cnt != 0).sum()) == Ai.nnz
+        assert cnt.numel() > dense.numel()          # a cheaper cell lets a larger rectangle pay
+        ci = ops.zeros_padded(n, f, "cuda")
+        ops.spmm(Ai, b1, ci, 0.0)
+        assert _rel(ci, cp) <= 1e-5
+        del Ai, ci, cnt
     # 1^T (A B) == (1^T A) B in fp64
     colsum = torch.zeros(n, dtype=torch.float64, device="cuda")
     colsum.index_add_(0, A.col.long(), A.val.double())

@@ -6,9 +6,11 @@ latency-critical loop that cannot afford the device-wide synchronisation `cudaMa
 The ordinary entry point needs a caller-allocated plan buffer; this one keeps the plan in a fixed device
 array inside the library and so allocates nothing.
 
-What is checked: its output against the ordinary entry point's on the same inputs, within the tolerance
-the other kernel tests use (1e-4 of the largest magnitude), for two calls in a row.  The second call uses a
-different matrix with fewer hub rows, so a list left over from the first call would show up as wrong rows.
+What is checked: its output against the ordinary entry point's on the same inputs and against an fp64 product
+from the CPU oracle's definition, within the tolerance the other kernel tests use (1e-4 of the largest
+magnitude), for two calls in a row.  The second call uses a different matrix with fewer hub rows, so a list left
+over from the first call would show up as wrong rows; and no device memory may have been taken between the
+moment before it and the moment after it (the first call is the warm-up that loads the module).
 This file is named to be collected last and does not depend on anything the other tests leave behind.
 """
 import ctypes
@@ -49,18 +51,26 @@ def _rel_err(got, want):
 def test_noalloc_matches_the_planned_entry_point_twice_in_a_row():
     cases = [(_block(3000, 12000, 12, hubs=6, seed=1), 41, 0.0),
              (_block(1500, 10000, 5, hubs=1, seed=2), 602, 1.0)]
-    for blk, f, beta in cases:
+    for call, (blk, f, beta) in enumerate(cases):
         A = ops.CsrBlock.from_coo(blk.rows, blk.cols, blk.vals, blk.n_rows, blk.n_cols)      # builds its own plan
         assert A.long_rows() >= 1
         g = torch.Generator().manual_seed(f)
-        B = ops.to_padded(torch.randn(blk.n_cols, f, generator=g).cuda())
+        Bh = torch.randn(blk.n_cols, f, generator=g)
+        B = ops.to_padded(Bh.cuda())
         C0 = torch.randn(blk.n_rows, f, generator=g).cuda()
         want = ops.to_padded(C0)
         ops.spmm(A, B, want, beta)                                                            # existing entry point
         got = ops.to_padded(C0)
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]
         _call_noalloc(A, B, got, beta)
         torch.cuda.synchronize()
+        if call > 0:                          # from the second call on the entry point takes no device memory at all
+            assert torch.cuda.mem_get_info()[0] == free_before
         assert _rel_err(got, want) <= REL
+        dense64 = torch.sparse_coo_tensor(torch.stack([blk.rows, blk.cols]), blk.vals.double(), (blk.n_rows, blk.n_cols))
+        oracle = torch.sparse.mm(dense64, Bh.double()) + beta * C0.double().cpu()
+        assert _rel_err(got.cpu(), oracle) <= REL
 
 
 def test_noalloc_rejects_sizes_beyond_its_scratch():
