@@ -578,7 +578,9 @@ static int launch_spmm_impl(const int* rowptr, const int* col, const float* val,
   cfg.dynamicSmemBytes = 0;
   cfg.stream = stream;
   cfg.attrs = attr;
-  cfg.numAttrs = (plan && g_tuning.spmm_overlap) ? 1 : 0;
+  // narrow B only: a wide row is several feature tiles, i.e. several blocks per hub row, and its tail is short; there the
+  // early start measured slightly slower (width 602 on the 233K-vertex graph: 15.54 against 15.40 ms all-sparse)
+  cfg.numAttrs = (plan && g_tuning.spmm_overlap && LPN < 32) ? 1 : 0;
   cudaError_t e;
   bool grouped = false;
   if constexpr (LPN < 32) grouped = g_tuning.spmm_group_avg > 0 && nnz <= static_cast<int64_t>(g_tuning.spmm_group_avg) * n;

@@ -140,6 +140,10 @@ def _row_major(t):
 # "tensor_cores": multiply the core with the tcgen05 kernel when the library was built with it (fp32 accuracy
 # through the hi/lo TF32 split, "3xTF32": 172 TFLOP/s fp32-equivalent against 40 for the fp32-FMA kernel); a dense
 # cell then costs a twelfth of a gathered nonzero and "density_tc" is the bar instead of "density".
+# "min_row_nnz": blocks with fewer nonzeros per row on average are left all-sparse whatever their hub rectangle looks
+# like: their multiply waits on the latency of scattered DRAM gathers, and taking the cheap, cache-resident hub
+# entries out of it saves nothing (R-MAT with 31 nonzeros per row, 4 M vertices, integer core worth 16 % of the
+# nonzeros: width 602 34.6 -> 36.2 ms, width 256 13.8 -> 14.4 ms).
 # "integer": a block that carries its normalisation factors (partition.Block.row_scale / col_scale) keeps its core
 # as the bf16 matrix of edge multiplicities between the two diagonals and multiplies it with three bf16 products
 # (csrc/core_gemm_int.cu): a quarter of the memory and a third of the tensor time of the 3xTF32 form, so the bar
@@ -148,7 +152,7 @@ CORE = {"enabled": os.environ.get("CAGNET_DENSE_CORE", "1") != "0", "density": 0
         "max_side": 16384, "max_bytes": 2 << 30, "min_share": 0.1, "min_width": 128, "rounds": 1,
         "tensor_cores": os.environ.get("CAGNET_CORE_TENSOR", "1") != "0",
         "integer": os.environ.get("CAGNET_CORE_INTEGER", "1") != "0", "density_int": 0.02, "max_side_int": 32768,
-        "min_width_int": 128}
+        "min_width_int": 128, "min_row_nnz": 64}
 
 
 def core_on_tensor_cores():
@@ -257,7 +261,7 @@ class CsrBlock:
         to CORE["rounds"] rectangles.  Runs once per block, with torch index kernels on the block's device; the
         choice depends only on the block (ties broken by index)."""
         cfg = CORE
-        if not cfg["enabled"]:
+        if not cfg["enabled"] or self.nnz < cfg["min_row_nnz"] * self.n:
             return
         integer = self.row_scale is not None and integer_core_available()
         if integer:
