@@ -33,6 +33,9 @@ constexpr int kNumSMs = 148;  // B200
 // k length of one tensor-core accumulation of the dense-core multiply (tuning knob "core_chunk")
 int core_chunk();
 int set_core_chunk(int value);
+// the same for the integer-core multiply (tuning knob "core_chunk_int")
+int core_chunk_int();
+int set_core_chunk_int(int value);
 
 
 }  // namespace cagnet

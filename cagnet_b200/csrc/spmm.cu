@@ -578,9 +578,9 @@ static int launch_spmm_impl(const int* rowptr, const int* col, const float* val,
   cfg.dynamicSmemBytes = 0;
   cfg.stream = stream;
   cfg.attrs = attr;
-  // narrow B only: a wide row is several feature tiles, i.e. several blocks per hub row, and its tail is short; there the
-  // early start measured slightly slower (width 602 on the 233K-vertex graph: 15.54 against 15.40 ms all-sparse)
-  cfg.numAttrs = (plan && g_tuning.spmm_overlap && LPN < 32) ? 1 : 0;
+  // Measured on one box, serialised against overlapped: 4 M-vertex R-MAT graph width 128 7.99 -> 6.95 ms, width 602
+  // 37.4 -> 36.8 ms; 233K-vertex graph width 602 with its dense core 10.14 -> 9.52 ms; width 16 0.78 -> 0.76 ms.
+  cfg.numAttrs = (plan && g_tuning.spmm_overlap) ? 1 : 0;
   cudaError_t e;
   bool grouped = false;
   if constexpr (LPN < 32) grouped = g_tuning.spmm_group_avg > 0 && nnz <= static_cast<int64_t>(g_tuning.spmm_group_avg) * n;
@@ -687,6 +687,10 @@ extern "C" int cagnet_set_param(const char* name, int value) {
     if (set_core_chunk(value)) return fail(CAGNET_E_ARG, "cagnet_set_param: core_chunk must be a multiple of 32, >= 256");
     return CAGNET_OK;
   }
+  if (!strcmp(name, "core_chunk_int")) {
+    if (set_core_chunk_int(value)) return fail(CAGNET_E_ARG, "cagnet_set_param: core_chunk_int must be a multiple of 64, >= 256");
+    return CAGNET_OK;
+  }
   if (!strcmp(name, "spmm_long_narrow")) {
     if (value < kMinLongThreshold) return fail(CAGNET_E_ARG, "cagnet_set_param: spmm_long_narrow must be >= 256");
     g_tuning.spmm_long_narrow = value;
@@ -735,6 +739,7 @@ extern "C" int cagnet_get_param(const char* name) {
   if (name && !strcmp(name, "spmm_overlap")) return g_tuning.spmm_overlap;
   if (name && !strcmp(name, "spmm_deep")) return g_tuning.spmm_deep;
   if (name && !strcmp(name, "core_chunk")) return core_chunk();
+  if (name && !strcmp(name, "core_chunk_int")) return core_chunk_int();
   return -1;
 }
 

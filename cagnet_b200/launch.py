@@ -40,6 +40,8 @@ def parse_args(algorithm, argv=None):
                    help="min_width: run every sparse product at the narrower of a layer's two widths")
     p.add_argument("--collective", type=str, default="all_gather", choices=["all_gather", "broadcast"],
                    help="1D: move H blocks with one all-gather per launch group, or one broadcast per source rank")
+    p.add_argument("--prefetch", type=str, default="True",
+                   help="1D all-gather schedule: post the next epoch's layer-1 feature gather under the current epoch")
     p.add_argument("--stagegroups", type=int, default=-1,
                    help="launch groups per sparse product (0 = one per stage, -1 = automatic)")
     args = p.parse_args(argv)
@@ -53,6 +55,7 @@ def parse_args(algorithm, argv=None):
     args.activations = args.activations == "True"
     args.accuracy = args.accuracy == "True"
     args.overlap = args.overlap == "True"
+    args.prefetch = args.prefetch == "True"
     if algorithm == "15d" and not args.replication:
         args.replication = 1
     if not args.accperrank:

@@ -381,7 +381,7 @@ def _core_multiply_int(core_int, B, ldb, C, ldc, f):
                                               ws.data_ptr(), ws.numel(), _stream()), "core_gemm_int")
     _native.check(L.cagnet_add_rows_scaled3_f32(D.data_ptr(), half, core_rows.data_ptr(), rs.data_ptr(), r, f,
                                                 C.data_ptr(), ldc, _stream()), "add_rows_scaled3")
-    chunk = _native.get_param("core_chunk")
+    chunk = _native.get_param("core_chunk_int")
     LAUNCHES[0] += 2 + (k + chunk - 1) // chunk
 
 

@@ -17,7 +17,8 @@ def main(argv=None):
     rank, size, device = launch.init_distributed(args)
     inputs, adj_matrix, data, features, classes = launch.load_inputs(args, device)
     rt = dist1d.Runtime(CudaBackend(device), args.activations, args.normalization, 1, args.timing, args.overlap,
-                        order=args.order, stage_groups=args.stagegroups, collective=args.collective)
+                        order=args.order, stage_groups=args.stagegroups, collective=args.collective,
+                        prefetch_features=args.prefetch and not args.timing)
     model = dist1d.run(rank, size, inputs, adj_matrix, data, features, classes, rt, args.epochs, args.midlayer,
                        args.runcount, args.accuracy, printer=lambda *a: print(*a, flush=True))
     return None if model is None else model.outputs

@@ -42,16 +42,21 @@ enum {
 int cagnet_version(void);
 const char* cagnet_last_error_string(void);
 
-/* Tuning knobs, for sweeps: "spmm_tile" (vectors per feature tile; 0 = automatic, which also picks the
- * two-vectors-per-lane mapping for products of 5..16 vectors), "spmm_rpb" (rows per thread block of the
- * warp-per-row kernel), "spmm_long" (rows with more nonzeros than this are listed in the plan and processed by a
- * whole thread block), "spmm_long_narrow" (a lower bound on that limit for products narrower than 128 columns;
- * equal to "spmm_long" by default), "spmm_group_avg" (blocks with at most this many nonzeros per row on average run
- * the lane-group kernel when B is narrower than 128 columns; 0 = never) and "spmm_group_max" (rows up to this length
- * are walked by one lane group there, longer ones by the whole warp; "spmm_group_pool" = consecutive rows per warp,
- * 0 = automatic; "spmm_overlap" = 1 lets the row kernel start under the tail of the hub-row kernel of the same multiply
- * through a programmatic dependent launch, 0 serialises them), "core_chunk" (k length of one tensor-core accumulation of the dense-core
- * multiply, a multiple of 32).  Host-side global state; returns CAGNET_E_ARG for an unknown name or value. */
+/* Tuning knobs, for sweeps (host-side global state; CAGNET_E_ARG for an unknown name or value):
+ *   "spmm_tile"        vectors per feature tile; 0 = automatic, which also picks the two-vectors-per-lane mapping for
+ *                      products of 5..16 vectors
+ *   "spmm_rpb"         rows (warps) per thread block of the row kernels
+ *   "spmm_long"        rows with more nonzeros than this are listed in the plan and processed by a whole thread block
+ *   "spmm_long_narrow" a lower bound on that limit for products narrower than 128 columns (= "spmm_long" by default)
+ *   "spmm_group_avg"   blocks with at most this many nonzeros per row on average run the lane-group kernel when B is
+ *                      narrower than 128 columns; 0 = never
+ *   "spmm_group_max"   rows up to this length are walked by one lane group there, longer ones by the whole warp
+ *   "spmm_group_pool"  consecutive rows per warp there; 0 = automatic
+ *   "spmm_deep"        1 = one-vector-per-lane products on such blocks issue their gathers in batches of 8
+ *   "spmm_overlap"     1 = the row kernel may start under the tail of the hub-row kernel of the same multiply
+ *                      (programmatic dependent launch); 0 serialises them
+ *   "core_chunk"       k length of one tensor-core accumulation of the 3xTF32 dense-core multiply (multiple of 32)
+ *   "core_chunk_int"   the same for the integer-core multiply (multiple of 64) */
 int cagnet_set_param(const char* name, int value);
 int cagnet_get_param(const char* name);
 
@@ -157,7 +162,7 @@ int cagnet_add_rows3_f32(const float* D, int64_t half, const int32_t* rows, int3
  *   cagnet_gather_scale_split3_bf16  out[k] = [y1 | y2 | y3] of cs[k] * B[idx[k], 0:f), K rows of 3*half bf16, half >= f
  *                                    rounded up to a multiple of 8 (columns [f, half) of every part zeroed).
  *   cagnet_core_gemm_int_bf16        D[R x 3*half] (fp32) = Cnt[R x K] (bf16, ld_cnt) . out, tcgen05 kind::f16 with
- *                                    fp32 accumulation, the k range cut into "core_chunk" pieces added in fp32.
+ *                                    fp32 accumulation, the k range cut into "core_chunk_int" pieces added in fp32.
  *                                    ws: cagnet_core_gemm_int_workspace_bytes.
  *   cagnet_add_rows_scaled3_f32      C[rows[i], n] += rs[i] * (D[i, n] + (D[i, half+n] + D[i, 2 half+n])), n < f.
  * All row starts 16-byte aligned.  cagnet_core_gemm_int_available() is 0 when the library was built without the

@@ -557,13 +557,13 @@ def test_integer_core_kernels_through_the_c_abi():
     cnt[0, :7] = 2.0
     D = torch.empty(R, 3 * half, device="cuda")
     ws = torch.empty(max(L.cagnet_core_gemm_int_workspace_bytes(R, K, f), 16), dtype=torch.uint8, device="cuda")
-    old_chunk = _native.get_param("core_chunk")
+    old_chunk = _native.get_param("core_chunk_int")
     try:
-        _native.set_param("core_chunk", 256)                               # two k chunks
+        _native.set_param("core_chunk_int", 256)                           # two k chunks
         _native.check(L.cagnet_core_gemm_int_bf16(cnt.data_ptr(), K, R, K, Ys.data_ptr(), half, D.data_ptr(), f,
                                                   ws.data_ptr(), ws.numel(), None), "core_gemm_int")
     finally:
-        _native.set_param("core_chunk", old_chunk)
+        _native.set_param("core_chunk_int", old_chunk)
     _close(D, cnt.double().cpu() @ Ys.double().cpu(), rel=1e-5)
     rows = torch.randperm(700, generator=g)[:R].int().cuda()
     rs = torch.rand(R, generator=g).cuda() + 0.1
