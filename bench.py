@@ -618,7 +618,8 @@ def run_algorithm(ctx, algo, args, workload, problem, data, f, classes, info, la
                                   "rate on graphs this dense, at the DRAM rate on the sparse ones"},
             "e2e": {"value": e2e_ms, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4},
             "gpu_launches": launches, "clocks": clocks, "loss": loss_resident, "loss_e2e": loss_host,
-            "multiplication_order": args.order, "stage_groups": args.stage_groups, "collective": args.collective,
+            "multiplication_order": args.order, "stage_groups": getattr(model, "launch_groups", args.stage_groups),
+            "collective": args.collective,
             "feature_prefetch": bool(getattr(rt, "prefetch_features", False)),
             "alt_order": alt, "dense_core": dense_core_info(model), "core_kernel": core_kernel,
             "core_kernel_built": "tcgen05" if _native.lib().cagnet_core_gemm_tc_available() == 1 else "sgemm",

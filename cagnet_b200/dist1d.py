@@ -18,6 +18,12 @@ import torch.nn.functional as F
 
 from . import partition
 from .backend import ACT_LOG_SOFTMAX, ACT_NONE, ACT_RELU
+
+
+def ops_pad_ld(f):
+    """Padded row length of an f-wide matrix (the rule of ops.pad_ld, restated so that this module does not need the
+    native library to be importable)."""
+    return (f + 3) // 4 * 4 if f <= 64 else (f + 31) // 32 * 32
 from .timing import CATEGORIES_15D, CATEGORIES_1D, Timers, all_gather_bytes, all_reduce_bytes
 
 
@@ -408,11 +414,20 @@ class Model:
                                                       degree_group=everyone)
         self.inputs_loc = be.as_matrix(inputs_loc)
         n_per_proc = int(math.ceil(float(node_count) / (size / c)))
-        # automatic launch groups: one.  Two groups put the communication of the second under the multiply of the
-        # first, but every group is a block of its own: its dense core is smaller and multiplies less efficiently,
-        # and each launch costs the same however little it does.  Measured on the 233K-vertex benchmark graph:
-        # 2 ranks 9.72 ms (one group) against 10.06 ms (two); 8 ranks 6.8 against 7.6 ms (before the dense core).
-        groups = rt.stage_groups if rt.stage_groups >= 0 else 1
+        # Automatic launch groups.  More groups put the communication of group g+1 under the multiply of group g, but
+        # every group is a block of its own: its dense core is smaller or gone, and each launch costs the same however
+        # little it does.  So: ONE group while a stage's H block is small (233K-vertex benchmark graph, 70-283 MB per
+        # stage: 2 ranks 9.72 ms with one group against 10.06 with two; 8 ranks 6.8 against 7.6), and pipelined
+        # groups once a stage moves half a gigabyte or more, where the gathers are the larger cost (1.33 B-edge graph,
+        # 1D: 4 ranks 95.0 -> 89.8 ms, 8 ranks 57.8 -> 48.3 ms with four groups; 14 M-vertex graph, 1.5D c = 2, 8 ranks:
+        # 42.5 -> 39.3 ms with one group per stage).  Every rank computes the same figure from global sizes.
+        if rt.stage_groups >= 0:
+            groups = rt.stage_groups
+        elif size > 1 and n_per_proc * ops_pad_ld(int(inputs.size(1))) * 4 >= (512 << 20):
+            groups = 4 if (c == 1 and rt.collective == "all_gather") else 0
+        else:
+            groups = 1
+        self.launch_groups = groups
         if c == 1 and size > 1 and rt.collective == "all_gather":
             self.am_pbyp = GatherPlan(be, blocks, rank, size, n_per_proc, groups)
             if rt.prefetch_features and dist.is_initialized() and rt.prefetch_group is None:
