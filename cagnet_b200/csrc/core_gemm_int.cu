@@ -17,12 +17,13 @@
 //                                D (+)= Cnt[:, k0:k0+kc) . Ys[k0:k0+kc)                     (fp32, R x 3 half)
 //   add_rows_scaled3_kernel      C[rows[i], n] += rs[i] * (D[i, n] + (D[i, half+n] + D[i, 2 half+n]))
 //
-// The k range is cut into chunks ("core_chunk_int", 8,192 by default) whose GEMMs add into D in their epilogue, a
-// proper fp32 addition; a tensor-core accumulator is not a round-to-nearest fp32 sum.  Every product Cnt * y is
-// exact here, so the only roundings are those of the accumulations, and the error grows far more slowly with the
-// chunk length than in the TF32 path (measured on a 30,720^2 core against fp64, largest error over largest
-// magnitude: chunks of 1,024 1.1e-7, 2,048 1.1e-7, 4,096 1.4e-7, 8,192 2.1e-7, the whole range in one 6.3e-7), while
-// every chunk costs a read and a write of the 224 MB scratch matrix (core multiply 4.17 / 3.37 / 3.04 / 3.04 / 2.90 ms).
+// The k range may be cut into chunks ("core_chunk_int") whose GEMMs add into D in their epilogue, a proper fp32
+// addition; a tensor-core accumulator is not a round-to-nearest fp32 sum.  Every product Cnt * y is exact here, so
+// the only roundings are those of the accumulations, and the error grows far more slowly with the chunk length than
+// in the TF32 path (measured on a 30,720^2 core against fp64, largest error over largest magnitude: chunks of 1,024
+// 1.1e-7, 2,048 1.1e-7, 4,096 1.4e-7, 8,192 2.1e-7, the whole range in one 6.3e-7), while every chunk costs a read
+// and a write of the 224 MB scratch matrix (core multiply 4.17 / 3.37 / 3.04 / 3.04 / 2.90 ms).  The default, 32,768,
+// is the largest side a core may have: one GEMM per multiply, 160 times inside the 1e-4 the results must meet.
 //
 // This file instantiates CUTLASS / CuTe templates (header tree found at build time) and adds the kernels around
 // them.  Without the header tree the multiply reports CAGNET_E_ARG and the host layer keeps the other core kernels.
@@ -91,7 +92,7 @@ add_rows_scaled3_kernel(const float* __restrict__ D, int64_t half, const int* __
   if (n + 3 < f) out[3] += s * (a.w + (b.w + c.w));
 }
 
-static int g_core_chunk_int = 8192;
+static int g_core_chunk_int = 32768;
 int core_chunk_int() { return g_core_chunk_int; }
 int set_core_chunk_int(int value) {
   if (value < 256 || value % 64) return 1;

@@ -40,7 +40,13 @@ constexpr int kPlanMagic = 0x0CA67E70;
 constexpr int kPlanHeaderInts = 8;   // [0] magic [1] count [2] threshold [3] capacity
 constexpr int kMinLongThreshold = 256;
 constexpr int kLongWarps = 16;
-constexpr int kStagePairs = 64;    // (col, val) pairs a warp parks in shared memory at a time
+// (col, val) pairs a warp parks in shared memory at a time: 32, or 64 where gathers are batched with 4 lanes per
+// nonzero (a batch of 8 per lane group needs 64 pairs).  Kept as small as the variant allows: shared memory is carved
+// out of the L1 cache, and the wide, bandwidth-bound products lost 5 % when every variant reserved 64.
+template <int LPN, bool DEEP>
+struct StagePairs {
+  static constexpr int value = (DEEP && LPN <= 4) ? 64 : 32;
+};
 
 // ------------------------------------------------------------------------------------------------
 template <int VEC>
@@ -139,7 +145,7 @@ __device__ __forceinline__ void accumulate_range_batched(const int* __restrict__
   constexpr int CH = (LPN <= 4) ? 64 : 32;         // pairs staged per chunk
   constexpr int PER = CH / G;                      // pairs one lane group consumes per chunk
   constexpr int BATCH = (NV >= 2) ? 4 : 8;         // gathers in flight per lane
-  static_assert(PER % BATCH == 0 && CH <= kStagePairs, "chunk / batch mismatch");
+  static_assert(PER % BATCH == 0 && CH == StagePairs<LPN, true>::value, "chunk / batch mismatch");
   const int sub = lane / LPN;
   auto load_pair = [&](int e) {
     int2 p = make_int2(0, 0);
@@ -295,7 +301,7 @@ __global__ void __launch_bounds__(kMaxRowsPerBlock * 32) spmm_warp_rows_kernel(
     const int* __restrict__ rowptr, const int* __restrict__ col, const float* __restrict__ val, int n,
     const float* __restrict__ B, int ldb, float* __restrict__ C, int ldc, int f_eff, int f, float beta,
     const int* __restrict__ plan, int min_threshold) {
-  __shared__ __align__(16) int2 stage[kMaxRowsPerBlock][kStagePairs];
+  __shared__ __align__(16) int2 stage[kMaxRowsPerBlock][StagePairs<LPN, DEEP>::value];
   const int warp = threadIdx.x >> 5;
   const int row = blockIdx.x * (blockDim.x >> 5) + warp;
   if (row >= n) return;                      // whole warps leave together; nothing below is block-wide
@@ -349,7 +355,7 @@ __global__ void __launch_bounds__(kMaxRowsPerBlock * 32) spmm_group_rows_kernel(
 #define CAGNET_GROUP_UNROLL 8
 #endif
   constexpr int UNROLL = (NV >= 2) ? CAGNET_GROUP_UNROLL / 2 : CAGNET_GROUP_UNROLL;
-  __shared__ __align__(16) int2 stage[kMaxRowsPerBlock][kStagePairs];
+  __shared__ __align__(16) int2 stage[kMaxRowsPerBlock][StagePairs<LPN, DEEP>::value];
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int row0 = (blockIdx.x * (blockDim.x >> 5) + warp) * pool;
@@ -461,7 +467,7 @@ __global__ void __launch_bounds__(kLongWarps * 32) spmm_block_rows_kernel(
     const int* __restrict__ plan, int min_threshold) {
   constexpr int TILE = LPN * VEC * NV;
   __shared__ float part[kLongWarps][TILE];
-  __shared__ __align__(16) int2 stage[kLongWarps][kStagePairs];
+  __shared__ __align__(16) int2 stage[kLongWarps][StagePairs<LPN, DEEP>::value];
   pdl_release_dependents();
   const int long_threshold = max(__ldg(plan + 2), min_threshold);
   const int count = min(__ldg(plan + 1), __ldg(plan + 3));
@@ -477,7 +483,8 @@ __global__ void __launch_bounds__(kLongWarps * 32) spmm_block_rows_kernel(
     const int start = __ldg(rowptr + row);
     const int end = __ldg(rowptr + row + 1);
     if (end - start <= long_threshold) continue;   // listed, but short enough for the warp-per-row pass at this width
-    const int per = (((end - start) + kLongWarps - 1) / kLongWarps + kStagePairs - 1) & ~(kStagePairs - 1);
+    constexpr int PAIRS = StagePairs<LPN, DEEP>::value;
+    const int per = (((end - start) + kLongWarps - 1) / kLongWarps + PAIRS - 1) & ~(PAIRS - 1);
     const int ws = min(end, start + warp * per);
     const int we = min(end, ws + per);
 
