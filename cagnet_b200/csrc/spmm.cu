@@ -110,13 +110,18 @@ __device__ __forceinline__ void store_row(float* __restrict__ cp, int column0, i
 // kernel's longest row (100K+ nonzeros in an R-MAT graph, one thread block) would otherwise be a tail during which
 // the rest of the GPU idles.  The row kernel is launched with programmatic stream serialisation: it may start as
 // soon as every block of the hub kernel has begun (`pdl_release_dependents`), and it does not complete before the
-// hub kernel has (`pdl_wait_for_primary`, executed before a thread exits), so that whatever follows in the stream
-// still sees both kernels finished.  Only the row kernel's FIRST block waits: a grid is complete when all its blocks
-// are, so one waiting block is enough to order the completions, and the other blocks leave at once instead of
-// holding their SM slots until the hub kernel's last row is done.  Without a preceding hub kernel both are no-ops.
+// hub kernel has (`pdl_waiter_block`), so that whatever follows in the stream
+// still sees both kernels finished.  The waiting is done by ONE EXTRA block appended to the row kernel's grid, which
+// does nothing else: a grid is complete when all its blocks are, so one waiting block is enough to order the
+// completions, and the working blocks leave at once instead of holding their SM slots until the hub kernel's last
+// row is done.  (Waiting at the end of a working block instead cost the row kernel 6 registers, 38 for 32, and with
+// them a quarter of its resident warps.)
 __device__ __forceinline__ void pdl_release_dependents() { asm volatile("griddepcontrol.launch_dependents;"); }
-__device__ __forceinline__ void pdl_wait_for_primary() {
-  if (blockIdx.x == 0 && blockIdx.y == 0) asm volatile("griddepcontrol.wait;" ::: "memory");
+// True for the appended block: its first thread waits for the hub kernel, all its threads then leave.
+__device__ __forceinline__ bool pdl_waiter_block(int waiter) {
+  if (!waiter || blockIdx.x != gridDim.x - 1) return false;
+  if (blockIdx.y == 0 && threadIdx.x == 0) asm volatile("griddepcontrol.wait;" ::: "memory");
+  return true;
 }
 
 // Accumulates sum_e val[e] * B[col[e], tile columns of this lane] over e in [start, end) into acc.
@@ -296,14 +301,16 @@ __device__ __forceinline__ int live_vectors(int tile0, int l, int f_eff) {
 
 constexpr int kMaxRowsPerBlock = 8;
 
-// One vector per lane without batching fits 32 registers, i.e. 64 resident warps per SM; the second launch-bounds
-// argument holds the compiler to that (at 38 registers the wide, memory-bound products measured 2-4 % slower).
+// (Holding this kernel to 32 registers with a second launch-bounds argument, for 64 instead of 48 resident warps per
+// SM, measured 5-7 % SLOWER on the wide, memory-bound products: the compiler pays for the registers with serialised
+// loads.)
 template <int VEC, int LPN, int NV, bool DEEP>
-__global__ void __launch_bounds__(kMaxRowsPerBlock * 32, (NV == 1 && !DEEP) ? 8 : 1) spmm_warp_rows_kernel(
+__global__ void __launch_bounds__(kMaxRowsPerBlock * 32) spmm_warp_rows_kernel(
     const int* __restrict__ rowptr, const int* __restrict__ col, const float* __restrict__ val, int n,
     const float* __restrict__ B, int ldb, float* __restrict__ C, int ldc, int f_eff, int f, float beta,
-    const int* __restrict__ plan, int min_threshold) {
+    const int* __restrict__ plan, int min_threshold, int waiter) {
   __shared__ __align__(16) int2 stage[kMaxRowsPerBlock][StagePairs<LPN, DEEP>::value];
+  if (pdl_waiter_block(waiter)) return;
   const int warp = threadIdx.x >> 5;
   const int row = blockIdx.x * (blockDim.x >> 5) + warp;
   if (row >= n) return;                      // whole warps leave together; nothing below is block-wide
@@ -313,10 +320,7 @@ __global__ void __launch_bounds__(kMaxRowsPerBlock * 32, (NV == 1 && !DEEP) ? 8 
   const int start = __ldg(rowptr + row);
   const int end = __ldg(rowptr + row + 1);
   const int long_threshold = plan ? max(__ldg(plan + 2), min_threshold) : INT_MAX;
-  if (end - start > long_threshold) {        // a hub row: the block-per-row kernel owns it
-    pdl_wait_for_primary();
-    return;
-  }
+  if (end - start > long_threshold) return;  // a hub row: the block-per-row kernel owns it
   const int nvalid = live_vectors<VEC, LPN, NV>(tile0, l, f_eff);
 
   float acc[NV][VEC];
@@ -329,7 +333,6 @@ __global__ void __launch_bounds__(kMaxRowsPerBlock * 32, (NV == 1 && !DEEP) ? 8 
 
   if (lane < LPN)
     store_row<VEC, LPN, NV>(C + static_cast<int64_t>(row) * ldc + tile0 + l * VEC, tile0 + l * VEC, f, nvalid, beta, acc);
-  pdl_wait_for_primary();
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -350,8 +353,9 @@ template <int VEC, int LPN, int NV, bool DEEP>
 __global__ void __launch_bounds__(kMaxRowsPerBlock * 32) spmm_group_rows_kernel(
     const int* __restrict__ rowptr, const int* __restrict__ col, const float* __restrict__ val, int n,
     const float* __restrict__ B, int ldb, float* __restrict__ C, int ldc, int f_eff, int f, float beta,
-    const int* __restrict__ plan, int min_threshold, int group_max, int pool) {
+    const int* __restrict__ plan, int min_threshold, int group_max, int pool, int waiter) {
   static_assert(LPN < 32, "the lane-group kernel needs at least two groups per warp");
+  if (pdl_waiter_block(waiter)) return;
   constexpr int G = 32 / LPN;
 #ifndef CAGNET_GROUP_UNROLL
 #define CAGNET_GROUP_UNROLL 8
@@ -459,7 +463,6 @@ __global__ void __launch_bounds__(kMaxRowsPerBlock * 32) spmm_group_rows_kernel(
     if (lane < LPN)
       store_row<VEC, LPN, NV>(C + static_cast<int64_t>(row0 + i) * ldc + column0, column0, f, nvalid, beta, acc);
   }
-  pdl_wait_for_primary();
 }
 
 template <int VEC, int LPN, int NV, bool DEEP>
@@ -578,7 +581,7 @@ static int launch_spmm_impl(const int* rowptr, const int* col, const float* val,
         rowptr, col, val, B, ldb, C, ldc, f_eff, f, beta, plan, min_threshold);
   }
   const int rows_per_block = g_tuning.spmm_rpb;
-  // the row kernel: allowed to start while the hub kernel's last rows are still running (see pdl_wait_for_primary)
+  // the row kernel: allowed to start while the hub kernel's last rows are still running (see pdl_waiter_block)
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
@@ -590,6 +593,7 @@ static int launch_spmm_impl(const int* rowptr, const int* col, const float* val,
   // Measured on one box, serialised against overlapped: 4 M-vertex R-MAT graph width 128 7.99 -> 6.95 ms, width 602
   // 37.4 -> 36.8 ms; 233K-vertex graph width 602 with its dense core 10.14 -> 9.52 ms; width 16 0.78 -> 0.76 ms.
   cfg.numAttrs = (plan && g_tuning.spmm_overlap) ? 1 : 0;
+  const int waiter = static_cast<int>(cfg.numAttrs);      // one block more, which only waits for the hub kernel
   cudaError_t e;
   bool grouped = false;
   if constexpr (LPN < 32) grouped = g_tuning.spmm_group_avg > 0 && nnz <= static_cast<int64_t>(g_tuning.spmm_group_avg) * n;
@@ -597,15 +601,15 @@ static int launch_spmm_impl(const int* rowptr, const int* col, const float* val,
     if (grouped) {
       const int pool = group_pool_rows(n);
       const int pools = (n + pool - 1) / pool;
-      cfg.gridDim = dim3((pools + rows_per_block - 1) / rows_per_block, tiles);
+      cfg.gridDim = dim3((pools + rows_per_block - 1) / rows_per_block + waiter, tiles);
       e = cudaLaunchKernelEx(&cfg, spmm_group_rows_kernel<VEC, LPN, NV, DEEP>, rowptr, col, val, n, B, ldb, C, ldc, f_eff, f,
-                             beta, plan, min_threshold, g_tuning.spmm_group_max, pool);
+                             beta, plan, min_threshold, g_tuning.spmm_group_max, pool, waiter);
     }
   }
   if (!grouped) {
-    cfg.gridDim = dim3((n + rows_per_block - 1) / rows_per_block, tiles);
+    cfg.gridDim = dim3((n + rows_per_block - 1) / rows_per_block + waiter, tiles);
     e = cudaLaunchKernelEx(&cfg, spmm_warp_rows_kernel<VEC, LPN, NV, DEEP>, rowptr, col, val, n, B, ldb, C, ldc, f_eff, f, beta,
-                           plan, min_threshold);
+                           plan, min_threshold, waiter);
   }
   if (e != cudaSuccess) {
     snprintf(last_error_buf(), 256, "cagnet_spmm_csr_f32: CUDA launch failed: %s", cudaGetErrorString(e));
