@@ -254,9 +254,12 @@ class CsrBlock:
 
         Rows and columns are ranked by degree; among the rectangles (top r rows) x (top c columns), r and c
         multiples of CORE["step"], the one with the largest `nonzeros inside - density * cells` is taken if that
-        figure is worth it.  Its entries become a dense r x c fp32 matrix (`self.core`, with the row and column
-        lists) that `spmm` multiplies with cagnet_core_gemm_f32; all other entries form `self.rest`, a CSR block
-        with its own hub-row plan.  The full block stays as it is for narrow products.  `rest` is searched again
+        figure is worth it.  Its entries become a dense r x c matrix -- fp32 values (`self.core`, with the row and
+        column lists; multiplied by the 3xTF32 or the fp32-FMA kernel), or, when the block carries its normalisation
+        factors and its values factor exactly, the bf16 matrix of edge multiplicities with the two factor vectors
+        (`self.core_int`; three bf16 tensor-core products) -- and all other entries form `self.rest`, a CSR block
+        with its own hub-row plan.  The full block stays as it is for narrow products.  Blocks with fewer than
+        CORE["min_row_nnz"] nonzeros per row on average are left alone.  `rest` is searched again
         (the region is L-shaped in a symmetric matrix: hub rows x many columns, then many rows x hub columns), up
         to CORE["rounds"] rectangles.  Runs once per block, with torch index kernels on the block's device; the
         choice depends only on the block (ties broken by index)."""
@@ -270,9 +273,6 @@ class CsrBlock:
             bar, side, cell = (cfg["density_tc"] if core_on_tensor_cores() else cfg["density"]), cfg["max_side"], 4
         choice = core_select.choose_core(self.rowptr, self.col, self.n, self.m, bar, cfg["step"], side,
                                          cfg["max_bytes"], cfg["min_share"], cell)
-        if choice is None and integer:
-            # nothing worth it at 2 bytes a cell: nothing at 4 either
-            return
         if choice is None:
             return
         dense, rest_rowptr, rest_col, rest_val = core_select.split_core(self.col, self.val, self.n, choice)
