@@ -1,4 +1,6 @@
 """Flag surface of the entry scripts: the reference's flags, its string booleans and its required-argument rule."""
+import os
+
 import pytest
 
 from cagnet_b200 import datasets, launch
@@ -31,3 +33,23 @@ def test_graph_names_resolve_to_the_reference_shapes():
         datasets.parse_spec("NoSuchGraph")
     x, edge, data, f, classes, info = datasets.load("er:n=200,deg=6,f=5,c=3", device="cpu")
     assert x.shape == (200, 5) and data.y.max() < 3 and data.train_mask.all() and info["edges"] == edge.size(1)
+
+
+def test_bench_arms_on_a_machine_without_a_gpu():
+    """The reference arm of bench.py is the CPU restatement and runs anywhere; the product arm refuses to run without
+    a CUDA device instead of falling back to anything."""
+    import json
+    import subprocess
+    import sys
+    import torch
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    ref = subprocess.run([sys.executable, "bench.py", "--impl", "reference", "--workload", "tiny", "--steps", "1",
+                          "--warmup", "0"], cwd=root, capture_output=True, text=True, timeout=300)
+    assert ref.returncode == 0, ref.stderr[-500:]
+    line = json.loads(ref.stdout.strip().splitlines()[-1])
+    assert line["impl"] == "reference" and line["metric"] == "gcn_epoch_ms" and line["value"] > 0
+    assert line["cpu_baseline"]["kind"] == "port" and line["e2e"]["h2d_bytes_per_step"] == 0
+    if not torch.cuda.is_available():
+        ours = subprocess.run([sys.executable, "bench.py", "--workload", "tiny"], cwd=root, capture_output=True,
+                              text=True, timeout=300)
+        assert ours.returncode != 0 and "no CPU fallback" in (ours.stderr + ours.stdout)
