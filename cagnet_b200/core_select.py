@@ -84,8 +84,9 @@ def split_core(col, val, n, choice):
 def integer_core(dense, row_scale, col_scale, limit=256):
     """The multiplicity matrix of a dense core whose block was scaled by two diagonals, or None.
 
-    `dense[i, j]` must equal fl32(row_scale[i] * fl32(cnt * col_scale[j])) bit for bit with cnt a non-negative
-    integer <= `limit` (the way partition.coalesce_block computes a normalised entry); then dense =
+    `dense[i, j]` must equal fl32(row_scale[i] * fl32(cnt * col_scale[j])) -- or, every cell, the other order
+    fl32(col_scale[j] * fl32(cnt * row_scale[i])) -- bit for bit with cnt a non-negative
+    integer <= `limit` (the two ways partition.coalesce_block computes a normalised entry); then dense =
     diag(row_scale) . cnt . diag(col_scale) and cnt is returned as an fp32 matrix.  Any cell that does not fit --
     scales that do not belong to this block, weighted edges -- makes the answer None and the caller keeps the
     fp32 values."""
@@ -97,5 +98,9 @@ def integer_core(dense, row_scale, col_scale, limit=256):
         return None
     back = row_scale[:, None] * (cnt * col_scale[None, :])
     if not bool(torch.equal(back, dense)):
-        return None
+        # the block of a transposed operator is scaled row factor first (coalesce_block(..., row_first=True))
+        del back
+        back = col_scale[None, :] * (cnt * row_scale[:, None])
+        if not bool(torch.equal(back, dense)):
+            return None
     return cnt

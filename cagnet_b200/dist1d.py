@@ -44,7 +44,8 @@ class Runtime:
     """Per-process settings: what the reference keeps in module globals (gcn_distr.py:53-64)."""
 
     def __init__(self, backend, activations=True, normalization=True, replication=1, timing=False, overlap=True,
-                 categories=None, order="reference", stage_groups=-1, collective="all_gather", prefetch_features=False):
+                 categories=None, order="reference", stage_groups=-1, collective="all_gather", prefetch_features=False,
+                 directed=False):
         if order not in ("reference", "min_width"):
             raise ValueError("order must be 'reference' or 'min_width'")
         if collective not in ("all_gather", "broadcast"):
@@ -68,6 +69,11 @@ class Runtime:
         # ones (a loader that refills a second buffer) and the event that marks them ready.
         self.prefetch_features = bool(prefetch_features)
         self.prefetch_group = None
+        # The reference multiplies by the forward pass's blocks again in the backward pass: exact when the
+        # adjacency matrix is symmetric (gcn_distr.py:326, gcn_distr_2d.py:683 "only true for undirected graphs").
+        # `directed` partitions the transposed operator as well and multiplies the backward pass by that: twice
+        # the adjacency storage, the true gradients for a graph whose edge list is not symmetric.
+        self.directed = bool(directed)
         self.next_features = None
         self.layer1_input = None
         cats = categories or (CATEGORIES_15D if replication > 1 else CATEGORIES_1D)
@@ -350,7 +356,9 @@ class GCNFunc(torch.autograd.Function):
                 agg = z
         ctx.save_for_backward(inputs, weight, out)
         ctx.agg = agg
-        ctx.args = (am_partitions, rank, size, group, row_groups, col_groups, act, rt)
+        # backward multiplies by the transposed operator's plan when the model built one (directed graphs)
+        ctx.args = (getattr(am_partitions, "backward_plan", None) or am_partitions, rank, size, group, row_groups,
+                    col_groups, act, rt)
         return out
 
     @staticmethod
@@ -428,13 +436,20 @@ class Model:
         else:
             groups = 1
         self.launch_groups = groups
-        if c == 1 and size > 1 and rt.collective == "all_gather":
-            self.am_pbyp = GatherPlan(be, blocks, rank, size, n_per_proc, groups)
-            if rt.prefetch_features and dist.is_initialized() and rt.prefetch_group is None:
-                # a communicator of its own: the prefetch must not queue in front of the epoch's other collectives
-                rt.prefetch_group = dist.new_group(list(range(size)))
-        else:
-            self.am_pbyp = StagePlan(be, blocks, rank, size, c, groups)
+        def make_plan(blks):
+            if c == 1 and size > 1 and rt.collective == "all_gather":
+                return GatherPlan(be, blks, rank, size, n_per_proc, groups)
+            return StagePlan(be, blks, rank, size, c, groups)
+
+        self.am_pbyp = make_plan(blocks)
+        if isinstance(self.am_pbyp, GatherPlan) and rt.prefetch_features and dist.is_initialized() \
+                and rt.prefetch_group is None:
+            # a communicator of its own: the prefetch must not queue in front of the epoch's other collectives
+            rt.prefetch_group = dist.new_group(list(range(size)))
+        if rt.directed:
+            _, blocks_t = partition.oned_partition(rank, size, inputs, adj_matrix, rt.normalization, c,
+                                                   degree_group=everyone, transposed=True)
+            self.am_pbyp.backward_plan = make_plan(blocks_t)
         rank_c = rank // c
         lo, hi = rank_c * n_per_proc, min(node_count, (rank_c + 1) * n_per_proc)
         dev = self.inputs_loc.device

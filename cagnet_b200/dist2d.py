@@ -29,13 +29,16 @@ from .timing import CATEGORIES_2D, Timers, all_gather_bytes, all_reduce_bytes
 
 class Runtime:
     def __init__(self, backend, activations=True, normalization=True, timing=False, overlap=True, cache_blocks=True,
-                 reference_label_alignment=True):
+                 reference_label_alignment=True, directed=False):
         self.backend = backend
         self.activations = bool(activations)
         self.normalization = bool(normalization)
         self.overlap = bool(overlap)
         self.cache_blocks = bool(cache_blocks)
         self.reference_label_alignment = bool(reference_label_alignment)
+        # backward pass multiplies by blocks of A^T instead of reusing A's (which is exact for undirected graphs
+        # only, gcn_distr_2d.py:683): a second set of adjacency blocks per process
+        self.directed = bool(directed)
         self.timers = Timers(CATEGORIES_2D, timing, getattr(backend, "synchronize", None))
 
 
@@ -65,6 +68,23 @@ class Grid:
         return self.col_groups[self.col] if self.comm else None
 
 
+class AdjOperator:
+    """One process's block of a sparse operator and what the stage loop keeps with it: the wire form it
+    broadcasts, the blocks received from the other processes of its row (kept after the first product), and the
+    nonzero count of every process's block (exchanged once, so that receive buffers can be sized)."""
+
+    def __init__(self, be, block, rank, count, group, device):
+        self.adj_block = be.make_block(block)
+        self.adj_wire = be.block_to_wire(self.adj_block) if group is not None else None
+        self.block_cache, self.blocks_sent = {}, False
+        nnz = torch.zeros(count, dtype=torch.int64)
+        nnz[rank] = be.block_nnz(self.adj_block)
+        if group is not None:
+            nnz = nnz.to(device)
+            dist.all_reduce(nnz, group=group)
+        self.nnz_of = [int(v) for v in nnz.tolist()]
+
+
 def _offsets(sizes):
     out = [0]
     for s in sizes:
@@ -77,12 +97,13 @@ def _bcast(tensor, src, group, async_op=False):
 
 
 # ------------------------------------------------------------------------------------------ SUMMA pieces
-def summa_sparse(model, inputs):
+def summa_sparse(model, inputs, op=None):
     """Z[row, col] = sum_k A[row, k] . H[k, col]   (gcn_distr_2d.py:286-426).
 
     Stage k: process (row, k) supplies A[row, k] to its process row, process (k, col) supplies H[k, col] to its
     process column.  The H broadcast of stage k+1 is posted before the multiply of stage k is queued."""
     rt, g, be = model.rt, model.grid, model.rt.backend
+    op = model if op is None else op          # whose block, wire form, cache and counts the stages use
     q = g.q
     inputs = be.as_matrix(inputs)
     f_col = inputs.size(1)
@@ -92,22 +113,22 @@ def summa_sparse(model, inputs):
     def a_block(k):
         src = g.row * q + k
         if src == g.rank:
-            blk = model.adj_block
-            if g.comm and not (rt.cache_blocks and model.blocks_sent):
-                with rt.timers.comm("a_block_broadcast", model.adj_wire.numel() * 4, "comm_time", "summa_sparse_bcast1"):
-                    _bcast(model.adj_wire, src, g.row_group)
-                rt.timers.count("summa_sparse_bcast1_words", model.adj_wire.numel())
+            blk = op.adj_block
+            if g.comm and not (rt.cache_blocks and op.blocks_sent):
+                with rt.timers.comm("a_block_broadcast", op.adj_wire.numel() * 4, "comm_time", "summa_sparse_bcast1"):
+                    _bcast(op.adj_wire, src, g.row_group)
+                rt.timers.count("summa_sparse_bcast1_words", op.adj_wire.numel())
             return blk
-        if rt.cache_blocks and k in model.block_cache:
-            return model.block_cache[k]
-        n_r, n_c, nnz = model.row_sizes[g.row], model.row_sizes[k], model.nnz_of[src]
+        if rt.cache_blocks and k in op.block_cache:
+            return op.block_cache[k]
+        n_r, n_c, nnz = model.row_sizes[g.row], model.row_sizes[k], op.nnz_of[src]
         buf = be.wire_buffer(n_r, nnz)
         with rt.timers.comm("a_block_broadcast", buf.numel() * 4, "comm_time", "summa_sparse_bcast1"):
             _bcast(buf, src, g.row_group)
         rt.timers.count("summa_sparse_bcast1_words", buf.numel())
         blk = be.block_from_wire(buf, n_r, n_c, nnz, reused=rt.cache_blocks)
         if rt.cache_blocks:
-            model.block_cache[k] = blk
+            op.block_cache[k] = blk
         return blk
 
     def post_h(k):
@@ -141,7 +162,7 @@ def summa_sparse(model, inputs):
                 work.wait()
         with rt.timers.region("comp_time", "summa_sparse_comp"):
             be.spmm(blk, tensor, z, 0.0 if k == 0 else 1.0)
-    model.blocks_sent = True
+    op.blocks_sent = True
     return z
 
 
@@ -293,8 +314,9 @@ class GCNFunc(torch.autograd.Function):
             dz = be.act_bwd(out, grad_output, ACT_RELU)
         else:
             dz = grad_output
-        # A is used as its own transpose: exact for undirected graphs only (gcn_distr_2d.py:683)
-        ag = summa_sparse(model, dz)
+        # A is used as its own transpose: exact for undirected graphs only (gcn_distr_2d.py:683); a model built
+        # with `directed` holds the blocks of A^T and multiplies by those
+        ag = summa_sparse(model, dz, model.adj_t)
         grad_input = summa_loc(model, ag, weight, transposed=True) if ctx.needs_input_grad[0] else None
         with rt.timers.region("transpose_time"):
             ht = transpose(model, inputs, weight.size(0))
@@ -342,6 +364,11 @@ class Model:
             nnz = nnz.to(self.inputs_loc.device)
             dist.all_reduce(nnz, group=g.group)
         self.nnz_of = [int(v) for v in nnz.tolist()]
+        self.adj_t = None
+        if rt.directed:
+            _, block_t = partition.twod_partition(rank, size, inputs, adj_matrix, rt.normalization,
+                                                  degree_group=everyone, transposed=True)
+            self.adj_t = AdjOperator(be, block_t, rank, q * q, g.group if g.comm else None, self.inputs_loc.device)
         self._setup_labels(data, n, classes)
 
     def _setup_labels(self, data, n, classes):

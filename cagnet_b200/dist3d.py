@@ -20,19 +20,20 @@ import torch.nn.functional as F
 from . import partition
 from .backend import ACT_LOG_SOFTMAX, ACT_NONE, ACT_RELU
 from .dist1d import Data, act_name  # noqa: F401
-from .dist2d import MaskedNLL, _bcast, _offsets
+from .dist2d import AdjOperator, MaskedNLL, _bcast, _offsets
 from .timing import CATEGORIES_3D, Timers, all_gather_bytes, all_reduce_bytes
 
 
 class Runtime:
     def __init__(self, backend, activations=False, normalization=False, timing=False, overlap=True, cache_blocks=True,
-                 reference_label_alignment=True):
+                 reference_label_alignment=True, directed=False):
         self.backend = backend
         self.activations = bool(activations)
         self.normalization = bool(normalization)
         self.overlap = bool(overlap)
         self.cache_blocks = bool(cache_blocks)
         self.reference_label_alignment = bool(reference_label_alignment)
+        self.directed = bool(directed)         # backward pass over slabs of A^T (the reference reuses A's)
         self.timers = Timers(CATEGORIES_3D, timing, getattr(backend, "synchronize", None))
 
 
@@ -74,9 +75,10 @@ def _column_chunk(be, z, sizes, k):
     return be.as_matrix(z[:, off[k]:off[k + 1]])
 
 
-def split3dspmm_sparse(model, inputs):
+def split3dspmm_sparse(model, inputs, op=None):
     """(A . H) block (i, j), column chunk k.  gcn_distr_3d.py:325-500."""
     rt, g, be = model.rt, model.grid, model.rt.backend
+    op = model if op is None else op          # whose block, wire form, cache and counts the stages use
     q = g.q
     inputs = be.as_matrix(inputs)
     f_j = inputs.size(1)
@@ -86,21 +88,21 @@ def split3dspmm_sparse(model, inputs):
     def a_slab(kp):
         src = g.rank_of(g.i, kp, g.k)
         if src == g.rank:
-            if g.comm and not (rt.cache_blocks and model.blocks_sent):
-                with rt.timers.comm("a_block_broadcast", model.adj_wire.numel() * 4, "comm_time", "summa_sparse_bcast1"):
-                    _bcast(model.adj_wire, src, g.row_group)
-                rt.timers.count("summa_sparse_bcast1_words", model.adj_wire.numel())
-            return model.adj_block
-        if rt.cache_blocks and kp in model.block_cache:
-            return model.block_cache[kp]
-        n_r, n_c, nnz = model.row_sizes[g.i], model.sub_sizes[kp][g.k], model.nnz_of[src]
+            if g.comm and not (rt.cache_blocks and op.blocks_sent):
+                with rt.timers.comm("a_block_broadcast", op.adj_wire.numel() * 4, "comm_time", "summa_sparse_bcast1"):
+                    _bcast(op.adj_wire, src, g.row_group)
+                rt.timers.count("summa_sparse_bcast1_words", op.adj_wire.numel())
+            return op.adj_block
+        if rt.cache_blocks and kp in op.block_cache:
+            return op.block_cache[kp]
+        n_r, n_c, nnz = model.row_sizes[g.i], model.sub_sizes[kp][g.k], op.nnz_of[src]
         buf = be.wire_buffer(n_r, nnz)
         with rt.timers.comm("a_block_broadcast", buf.numel() * 4, "comm_time", "summa_sparse_bcast1"):
             _bcast(buf, src, g.row_group)
         rt.timers.count("summa_sparse_bcast1_words", buf.numel())
         blk = be.block_from_wire(buf, n_r, n_c, nnz, reused=rt.cache_blocks)
         if rt.cache_blocks:
-            model.block_cache[kp] = blk
+            op.block_cache[kp] = blk
         return blk
 
     def post_h(kp):
@@ -134,7 +136,7 @@ def split3dspmm_sparse(model, inputs):
                 work.wait()
         with rt.timers.region("comp_time", "summa_sparse_comp"):
             be.spmm(blk, tensor, z, 0.0 if kp == 0 else 1.0)
-    model.blocks_sent = True
+    op.blocks_sent = True
     if g.comm:
         with rt.timers.comm("z_fiber_all_reduce", all_reduce_bytes(be.wire(z).numel() * 4, q), "comm_time",
                             "summa_sparse_reduce"):
@@ -306,7 +308,7 @@ class GCNFunc(torch.autograd.Function):
             dz = be.act_bwd(out, grad_output, ACT_RELU)
         else:
             dz = grad_output
-        ag = split3dspmm_sparse(model, dz)
+        ag = split3dspmm_sparse(model, dz, model.adj_t)         # A's own slabs unless the model is `directed`
         grad_input = split3dspmm_loc(model, ag, weight, transposed=True) if ctx.needs_input_grad[0] else None
         with rt.timers.region("transpose_time"):
             ag_t = transpose(model, ag, weight.size(1))
@@ -338,6 +340,11 @@ class Model:
             nnz = nnz.to(self.inputs_loc.device)
             dist.all_reduce(nnz, group=g.group)
         self.nnz_of = [int(v) for v in nnz.tolist()]
+        self.adj_t = None
+        if rt.directed:
+            _, slab_t = partition.threed_partition(rank, size, inputs, adj_matrix, rt.normalization,
+                                                   degree_group=g.group if g.comm else None, transposed=True)
+            self.adj_t = AdjOperator(be, slab_t, rank, size, g.group if g.comm else None, self.inputs_loc.device)
         self._setup_labels(data, n, classes)
 
     def _setup_labels(self, data, n, classes):

@@ -42,6 +42,9 @@ def parse_args(algorithm, argv=None):
                    help="1D: move H blocks with one all-gather per launch group, or one broadcast per source rank")
     p.add_argument("--prefetch", type=str, default="True",
                    help="1D all-gather schedule: post the next epoch's layer-1 feature gather under the current epoch")
+    p.add_argument("--directed", type=str, default="False",
+                   help="backward pass over the transposed adjacency blocks (a second copy of the graph): the true "
+                        "gradients for an edge list that is not symmetric; the reference reuses the forward blocks")
     p.add_argument("--stagegroups", type=int, default=-1,
                    help="launch groups per sparse product (0 = one per stage, -1 = automatic)")
     args = p.parse_args(argv)
@@ -56,6 +59,7 @@ def parse_args(algorithm, argv=None):
     args.accuracy = args.accuracy == "True"
     args.overlap = args.overlap == "True"
     args.prefetch = args.prefetch == "True"
+    args.directed = args.directed == "True"
     if algorithm == "15d" and not args.replication:
         args.replication = 1
     if not args.accperrank:

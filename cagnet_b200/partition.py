@@ -66,16 +66,17 @@ def inv_sqrt_degree(adj, node_count, group=None):
     return deg.double().pow(-0.5).float()
 
 
-def coalesce_block(r, c, n_rows, n_cols, d_row=None, d_col=None):
+def coalesce_block(r, c, n_rows, n_cols, d_row=None, d_col=None, row_first=False):
     """Entries (r, c) -> Block; duplicate entries add up (value = multiplicity) as `.coalesce()` does, then
     val = d_row[r] * (val * d_col[c]): the two diagonal products of scale_elements (gcn_distr.py:458-464),
-    one fp32 rounding each."""
+    one fp32 rounding each.  `row_first` applies the row factor first, d_col[c] * (val * d_row[r]): the
+    transposed block of a directed graph then holds bit for bit the values of the block it transposes."""
     key, counts = torch.unique(r * n_cols + c, return_counts=True)
     rows = torch.div(key, n_cols, rounding_mode="floor")
     cols = key - rows * n_cols
     vals = counts.to(torch.float32)
     if d_row is not None:
-        vals = d_row[rows] * (vals * d_col[cols])
+        vals = d_col[cols] * (vals * d_row[rows]) if row_first else d_row[rows] * (vals * d_col[cols])
         return Block(rows, cols, vals, int(n_rows), int(n_cols), d_row.contiguous(), d_col.contiguous())
     return Block(rows, cols, vals, int(n_rows), int(n_cols))
 
@@ -106,28 +107,34 @@ def _in_range(x, lo, hi):
 
 
 # ------------------------------------------------------------------------------------------ 1D / 1.5D
-def oned_partition(rank, size, inputs, adj, normalization=True, replication=1, degree_group=None):
+def oned_partition(rank, size, inputs, adj, normalization=True, replication=1, degree_group=None, transposed=False):
     """Blocks and feature rows of one rank for the 1D (replication = 1, gcn_distr.py:472-522) and 1.5D
     (gcn_distr_15d.py:497-549) algorithms.  blocks[i] is what the layer multiplies by H_i: the
-    transpose of A[rows_i, cols_rank], coalesced (gcn_distr.py:546), n_rank x n_i."""
+    transpose of A[rows_i, cols_rank], coalesced (gcn_distr.py:546), n_rank x n_i.
+
+    `transposed` (not in the reference, which multiplies by the same blocks in the backward pass and is exact
+    for undirected graphs only) gives the blocks of the TRANSPOSED operator, A[rows_rank, cols_i] itself, with
+    the same degree factors: what the backward pass of a directed graph has to multiply by."""
     n = inputs.size(0)
     n_per_proc = math.ceil(float(n) / (size / replication))
     rank_c = rank // replication
     vtx = boundaries(n, n_per_proc)
     lo, hi = vtx[rank_c], vtx[rank_c + 1]
     d = inv_sqrt_degree(adj, n, degree_group) if normalization else None
+    a0, a1 = (adj[1], adj[0]) if transposed else (adj[0], adj[1])
     if lo == 0 and hi == n:
-        u, v = adj[0], adj[1]                 # one block row: nothing to filter (and no 2 x E copy at 1.3 G edges)
+        u, v = a0, a1                         # one block row: nothing to filter (and no 2 x E copy at 1.3 G edges)
     else:
-        sel = _in_range(adj[1], lo, hi)
-        u, v = adj[0][sel], adj[1][sel] - lo
+        sel = _in_range(a1, lo, hi)
+        u, v = a0[sel], a1[sel] - lo
     blocks = []
     for i in range(len(vtx) - 1):
         s = slice(None) if len(vtx) == 2 else _in_range(u, vtx[i], vtx[i + 1])
         n_i = vtx[i + 1] - vtx[i]
         # stored orientation: row = column vertex of A (local to this rank), column = row vertex (local to block i)
         if normalization:
-            blocks.append(coalesce_block(v[s], u[s] - vtx[i], hi - lo, n_i, d[lo:hi], d[vtx[i]:vtx[i + 1]]))
+            blocks.append(coalesce_block(v[s], u[s] - vtx[i], hi - lo, n_i, d[lo:hi], d[vtx[i]:vtx[i + 1]],
+                                         row_first=transposed))
         else:
             blocks.append(coalesce_block(v[s], u[s] - vtx[i], hi - lo, n_i))
     inputs_loc = inputs[lo:hi]
@@ -157,19 +164,21 @@ def grid_side_2d(size):
     return math.floor(math.sqrt(size))
 
 
-def twod_partition(rank, size, inputs, adj, normalization=True, q=None, degree_group=None):
+def twod_partition(rank, size, inputs, adj, normalization=True, q=None, degree_group=None, transposed=False):
     """Block (rank_row, rank_col) of A -- not transposed -- and of H (rows and feature columns floor-split,
-    remainder last): gcn_distr_2d.py:1093-1164."""
+    remainder last): gcn_distr_2d.py:1093-1164.  `transposed` (not in the reference): the same block of A^T, the
+    operator of a directed graph's backward pass, with the degree factors of A."""
     n = inputs.size(0)
     q = grid_side_2d(size) if q is None else q
     rank_row, rank_col = rank // q, rank % q
     vtx = boundaries(n, n // q, keep=q)
     r0, r1, c0, c1 = vtx[rank_row], vtx[rank_row + 1], vtx[rank_col], vtx[rank_col + 1]
-    sel = _in_range(adj[0], r0, r1) & _in_range(adj[1], c0, c1)
-    u, v = adj[0][sel] - r0, adj[1][sel] - c0
+    a0, a1 = (adj[1], adj[0]) if transposed else (adj[0], adj[1])
+    sel = _in_range(a0, r0, r1) & _in_range(a1, c0, c1)
+    u, v = a0[sel] - r0, a1[sel] - c0
     if normalization:
         d = inv_sqrt_degree(adj, n, degree_group)
-        block = coalesce_block(u, v, r1 - r0, c1 - c0, d[r0:r1], d[c0:c1])
+        block = coalesce_block(u, v, r1 - r0, c1 - c0, d[r0:r1], d[c0:c1], row_first=transposed)
     else:
         block = coalesce_block(u, v, r1 - r0, c1 - c0)
     fs = [0]
@@ -198,13 +207,14 @@ def coords_3d(rank, q):
     return (rank // q) // q, (rank // q) % q, rank % q
 
 
-def threed_partition(rank, size, inputs, adj, normalization=False, degree_group=None):
+def threed_partition(rank, size, inputs, adj, normalization=False, degree_group=None, transposed=False):
     """2D block (i, j), then its columns cut into c slabs and the H block's rows into c chunks; this rank keeps
     slab / chunk k (gcn_distr_3d.py:1533-1542, 1341-1382).  The reference never normalises here
     (gcn_distr_3d.py:66); `normalization=True` is this package's extension and scales exactly as 2D does."""
     q = grid_side_3d(size)
     i, j, k = coords_3d(rank, q)
-    inputs_2d, blk = twod_partition(i * q + j, q * q, inputs, adj, normalization, q=q, degree_group=degree_group)
+    inputs_2d, blk = twod_partition(i * q + j, q * q, inputs, adj, normalization, q=q, degree_group=degree_group,
+                                    transposed=transposed)
     vtx = boundaries(blk.n_cols, blk.n_cols // q, keep=q)
     s = _in_range(blk.cols, vtx[k], vtx[k + 1])
     # the reference rebuilds the slab from the coalesced indices with unit values (gcn_distr_3d.py:1357-1364)

@@ -18,7 +18,7 @@ def main(argv=None):
     inputs, adj_matrix, data, features, classes = launch.load_inputs(args, device)
     rt = dist1d.Runtime(CudaBackend(device), args.activations, args.normalization, 1, args.timing, args.overlap,
                         order=args.order, stage_groups=args.stagegroups, collective=args.collective,
-                        prefetch_features=args.prefetch and not args.timing)
+                        prefetch_features=args.prefetch and not args.timing, directed=args.directed)
     model = dist1d.run(rank, size, inputs, adj_matrix, data, features, classes, rt, args.epochs, args.midlayer,
                        args.runcount, args.accuracy, printer=lambda *a: print(*a, flush=True))
     return None if model is None else model.outputs

@@ -18,7 +18,8 @@ def main(argv=None):
         raise SystemExit("the process count must be a multiple of the replication factor")
     inputs, adj_matrix, data, features, classes = launch.load_inputs(args, device)
     rt = dist1d.Runtime(CudaBackend(device), args.activations, args.normalization, args.replication, args.timing,
-                        args.overlap, order=args.order, stage_groups=args.stagegroups, collective=args.collective)
+                        args.overlap, order=args.order, stage_groups=args.stagegroups, collective=args.collective,
+                        directed=args.directed)
     model = dist1d.run(rank, size, inputs, adj_matrix, data, features, classes, rt, args.epochs, args.midlayer,
                        args.runcount, args.accuracy, printer=lambda *a: print(*a, flush=True))
     return None if model is None else model.outputs

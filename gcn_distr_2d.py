@@ -15,7 +15,8 @@ def main(argv=None):
     rank, size, device = launch.init_distributed(args)
     inputs, adj_matrix, data, features, classes = launch.load_inputs(args, device)
     print("Processes: " + str(size), flush=True)
-    rt = dist2d.Runtime(CudaBackend(device), args.activations, args.normalization, args.timing, args.overlap)
+    rt = dist2d.Runtime(CudaBackend(device), args.activations, args.normalization, args.timing, args.overlap,
+                        directed=args.directed)
     grid = dist2d.Grid(rank, size)
     if not grid.active:                               # surplus ranks beyond the square grid do nothing
         return None

@@ -14,7 +14,8 @@ def main(argv=None):
     rank, size, device = launch.init_distributed(args)
     inputs, adj_matrix, data, features, classes = launch.load_inputs(args, device)
     print("Processes: " + str(size), flush=True)
-    rt = dist3d.Runtime(CudaBackend(device), args.activations, args.normalization, args.timing, args.overlap)
+    rt = dist3d.Runtime(CudaBackend(device), args.activations, args.normalization, args.timing, args.overlap,
+                        directed=args.directed)
     grid = dist3d.Grid(rank, size)
     print("Before partitioning...", flush=True)
     model = dist3d.Model(rt, rank, size, inputs, adj_matrix, data, features, classes, grid)

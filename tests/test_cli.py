@@ -17,6 +17,10 @@ def test_reference_flags_parse():
     c = launch.parse_args("3d", ["--accperrank=8", "--epochs=5", "--graphname=subgraph3", "--timing=False",
                                  "--midlayer=16"])
     assert c.runcount == 1 and c.normalization is False and c.activations is False    # the reference's 3D model
+    assert a.directed is False and c.directed is False               # the reference's backward unless asked
+    d = launch.parse_args("2d", ["--epochs=2", "--graphname=Cora", "--timing=False", "--midlayer=16", "--runcount=1",
+                                 "--directed=True"])
+    assert d.directed is True
 
 
 def test_missing_required_argument_exits():

@@ -111,3 +111,8 @@ def test_integer_core_recovers_multiplicities_exactly():
     assert core_select.integer_core(weighted, rs, cs) is None
     big = rs[:, None] * (cnt * 300 * cs[None, :])
     assert core_select.integer_core(big, rs, cs) is None            # multiplicity beyond what bf16 holds exactly
+    # the block of a transposed operator is scaled in the other order; it differs in some last bits and is accepted
+    other = cs[None, :] * (cnt * rs[:, None])
+    assert not torch.equal(other, dense)
+    got = core_select.integer_core(other, rs, cs)
+    assert got is not None and torch.equal(got, cnt)

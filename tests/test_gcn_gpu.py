@@ -157,3 +157,44 @@ def test_captured_epoch_replays_to_the_same_numbers(golden_dir):
         assert _rel(out.detach(), d[f"r0_ep{ep}_out"]) <= 1e-4, ep
         assert _rel(model.weight1.detach(), d[f"r0_ep{ep}_w1"]) <= 1e-4, ep
         assert _rel(model.weight2.grad, d[f"r0_ep{ep}_gw2"]) <= 1e-4, ep
+
+
+@pytest.mark.parametrize("algo", ["1d", "1d_min_width", "2d", "3d"])
+def test_directed_graph_on_one_gpu(algo):
+    """`directed=True` on the CUDA path: the backward pass multiplies by the transposed operator's blocks, and the
+    gradients are those of fp64 autograd through the dense model on an edge list that is NOT symmetric (the
+    reference's backward, which reuses the forward blocks, is exact for undirected graphs only:
+    gcn_distr.py:326, gcn_distr_2d.py:683)."""
+    from cagnet_b200 import dist1d, dist2d, dist3d, graphs
+    from cagnet_b200.backend import CudaBackend
+    from tests import test_directed_gloo as D
+    edge, x, y, mask = D._problem()
+    adj = graphs.add_self_loops(edge, D.N)
+    data = dist1d.Data(y=y, train_mask=mask)
+    if algo.startswith("1d"):
+        rt = dist1d.Runtime(CudaBackend(), True, True, order="min_width" if algo == "1d_min_width" else "reference",
+                            directed=True)
+        model = dist1d.Model(rt, 0, 1, x, adj, data, D.F_IN, D.CLASSES)
+        m = D._dense_operator(adj, True).t()
+    elif algo == "2d":
+        rt = dist2d.Runtime(CudaBackend(), True, True, reference_label_alignment=False, directed=True)
+        model = dist2d.Model(rt, 0, 1, x, adj, data, D.F_IN, D.CLASSES)
+        m = D._dense_operator(adj, True)
+    else:
+        rt = dist3d.Runtime(CudaBackend(), activations=True, normalization=True, reference_label_alignment=False,
+                            directed=True)
+        model = dist3d.Model(rt, 0, 1, x, adj, data, D.F_IN, D.CLASSES)
+        m = D._dense_operator(adj, True)
+    want = D._expect(m, x, y, mask, [torch.arange(D.N)])
+    model.init_weights(D.MID)
+    for ep in range(D.EPOCHS):
+        out = model.train()
+        assert _rel(out.detach(), want[f"ep{ep}_out"]) <= 1e-4, (algo, ep, "out")
+        assert _rel(model.weight1.grad, want[f"ep{ep}_gw1"]) <= 1e-4, (algo, ep, "gw1")
+        assert _rel(model.weight2.grad, want[f"ep{ep}_gw2"]) <= 1e-4, (algo, ep, "gw2")
+    # without the flag the first weight gradient is off by far more than rounding on this graph
+    if algo == "1d":
+        plain = dist1d.Model(dist1d.Runtime(CudaBackend(), True, True), 0, 1, x, adj, data, D.F_IN, D.CLASSES)
+        plain.init_weights(D.MID)
+        plain.train()
+        assert _rel(plain.weight1.grad, want["ep0_gw1"]) > 1e-3

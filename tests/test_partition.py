@@ -145,3 +145,44 @@ def test_generators_are_seeded_and_symmetric():
     t = graphs.rmat_graph(1000, target_nnz=30000, seed=9)
     nnz = t.size(1) + 1000
     assert 0.985 * 30000 <= nnz <= 1.005 * 30000
+
+
+@pytest.mark.parametrize("normalization", [True, False])
+def test_transposed_blocks_are_the_exact_transpose(normalization):
+    """`transposed=True` of each partitioner, assembled over all ranks, is the transpose of what the plain call
+    assembles to -- bit for bit, on an edge list that is not symmetric and has duplicates."""
+    g = torch.Generator().manual_seed(5)
+    n, f = 37, 6
+    edge = torch.randint(0, n, (2, 300), generator=g)
+    edge = torch.cat([edge, edge[:, :20]], dim=1)                   # duplicates: multiplicities above one
+    adj = graphs.add_self_loops(edge, n) if normalization else edge
+    x = torch.randn(n, f, generator=g)
+
+    def dense(b):
+        return torch.sparse_coo_tensor(torch.stack([b.rows, b.cols]), b.vals, (b.n_rows, b.n_cols)).to_dense()
+
+    def oned(P, c, t):
+        rows = [torch.cat([dense(b) for b in PP.oned_partition(r, P, x, adj, normalization, c, transposed=t)[1]], dim=1)
+                for r in range(0, P, c)]
+        return torch.cat(rows, dim=0)
+
+    def twod(P, t):
+        q = PP.grid_side_2d(P)
+        return torch.cat([torch.cat([dense(PP.twod_partition(i * q + j, P, x, adj, normalization, transposed=t)[1])
+                                     for j in range(q)], dim=1) for i in range(q)], dim=0)
+
+    def threed(t, q=2):
+        return torch.cat([torch.cat([dense(PP.threed_partition((i * q + j) * q + k, q ** 3, x, adj, normalization,
+                                                               transposed=t)[1])
+                                     for j in range(q) for k in range(q)], dim=1) for i in range(q)], dim=0)
+
+    for P, c in ((1, 1), (3, 1), (4, 2)):
+        assert torch.equal(oned(P, c, True), oned(P, c, False).t())
+    assert not torch.equal(oned(3, 1, False), oned(3, 1, False).t())        # the graph really is directed
+    for P in (4, 9):
+        assert torch.equal(twod(P, True), twod(P, False).t())
+    assert torch.equal(threed(True), threed(False).t())
+    if normalization:
+        # the scale vectors travel with the transposed blocks (the integer dense core needs them)
+        b = PP.twod_partition(1, 4, x, adj, True, transposed=True)[1]
+        assert b.row_scale.numel() == b.n_rows and b.col_scale.numel() == b.n_cols
