@@ -95,3 +95,42 @@ def test_loaded_graph_feeds_the_partitioner(tmp_path):
     adj = graphs.add_self_loops(edge, n)
     deg = partition.inv_sqrt_degree(adj, n)
     assert deg.shape == (n,) and bool(torch.isfinite(deg).all())
+
+
+def _accuracy_worker(rank, world, directory):
+    """The 1D driver on the raw Reddit pair, `--accuracy=True` (gcn_distr.py:654-661): returns what it printed and
+    this rank's output rows."""
+    from cagnet_b200 import datasets, dist1d, graphs
+    from oracle.cpu_backend import CpuBackend
+    x, edge, data, f, classes, _ = datasets.load("npz:dir=%s" % directory)
+    adj = graphs.add_self_loops(edge, x.size(0))
+    rt = dist1d.Runtime(CpuBackend(), True, True)
+    lines = []
+    model = dist1d.run(rank, world, x, adj, data, f, classes, rt, epochs=3, mid_layer=5, run_count=1, accuracy=True,
+                       printer=lambda *a: lines.append(" ".join(str(v) for v in a)))
+    return lines, model.outputs.detach().numpy().copy()
+
+
+def test_accuracy_line_from_loaded_splits(tmp_path):
+    """Train / validation / test accuracy of the driver's last line, computed from the splits the loader read,
+    equals the accuracy of the assembled per-rank outputs over the same splits."""
+    from tests.mp_util import run_ranks
+    n, f, classes, world = 90, 5, 3, 3
+    rng = np.random.default_rng(3)
+    label = rng.integers(0, classes, n)
+    node_types = rng.integers(1, 4, n)
+    np.savez(str(tmp_path / "reddit_data.npz"), feature=rng.standard_normal((n, f)), label=label, node_types=node_types)
+    row, col = rng.integers(0, n, 600), rng.integers(0, n, 600)
+    both = sp.coo_matrix((np.ones(1200), (np.concatenate([row, col]), np.concatenate([col, row]))), shape=(n, n))
+    sp.save_npz(str(tmp_path / "reddit_graph.npz"), both)
+
+    results = run_ranks(world, _accuracy_worker, str(tmp_path))
+    outputs = np.concatenate([results[r][1] for r in range(world)], axis=0)
+    assert outputs.shape == (n, classes)
+    pred = outputs.argmax(axis=1)
+    want = [float((pred[node_types == k] == label[node_types == k]).mean()) for k in (1, 2, 3)]
+    for lines, _ in results:
+        last = [ln for ln in lines if ln.startswith("Epoch: 900")]
+        assert len(last) == 1
+        got = [float(part.split(":")[1]) for part in last[0].split(",")[1:]]
+        assert got == pytest.approx(want, abs=1e-4)
