@@ -16,6 +16,12 @@ COMMON = ["--accperrank=1", "--epochs=3", "--graphname=er:n=3000,deg=8,f=20,c=6,
     ("gcn_distr_15d", ["--runcount=1", "--normalization=True", "--activations=True", "--replication=1"], 6),
     ("gcn_distr_2d", ["--runcount=1", "--normalization=True", "--activations=True", "--accuracy=True"], 6),
     ("gcn_distr_3d", [], 6),
+    # backward over the transposed blocks (this package's flag), every script
+    ("gcn_distr", ["--runcount=1", "--normalization=True", "--activations=True", "--directed=True"], 6),
+    ("gcn_distr_15d", ["--runcount=1", "--normalization=True", "--activations=True", "--replication=1",
+                       "--directed=True"], 6),
+    ("gcn_distr_2d", ["--runcount=1", "--normalization=True", "--activations=True", "--directed=True"], 6),
+    ("gcn_distr_3d", ["--directed=True"], 6),
 ])
 def test_script_runs_and_reports(script, extra, width, capsys, monkeypatch):
     for var in ("RANK", "WORLD_SIZE", "LOCAL_RANK"):
