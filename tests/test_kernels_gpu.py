@@ -533,6 +533,33 @@ def test_spmm_with_integer_core_matches_oracle(f, beta):
         ops.configure_core(**old)
 
 
+def test_transposed_block_keeps_its_integer_core():
+    """The block of the transposed operator (backward pass of a directed graph) is scaled row factor first; it still
+    factors into diag . multiplicities . diag, keeps the bf16 core, and multiplies as the fp64 transpose does."""
+    if not ops.integer_core_available():
+        pytest.skip("library built without the tensor-core kernels")
+    n, f = 4096, 130
+    edge = graphs.rmat_graph(n, target_nnz=n * 160, seed=5)
+    g = torch.Generator().manual_seed(2)
+    edge = edge[:, torch.rand(edge.size(1), generator=g) < 0.6]      # drop 40 % of the arcs: no longer symmetric
+    adj = graphs.add_self_loops(edge, n)
+    fwd = PP.oned_partition(0, 1, torch.zeros(n, 1), adj, True)[1][0]
+    bwd = PP.oned_partition(0, 1, torch.zeros(n, 1), adj, True, transposed=True)[1][0]
+    D = _dense64(fwd).to_dense()
+    assert not torch.equal(D, D.t()) and bwd.vals.numel() >= 80 * n    # above the rows-per-nonzero bar of the core
+    assert torch.equal(_dense64(bwd).to_dense(), D.t())
+    old = ops.configure_core(enabled=True, step=64, max_side_int=2048, min_share=0.0, density_int=0.05, min_width_int=16)
+    try:
+        A = ops.CsrBlock.from_coo(bwd.rows, bwd.cols, bwd.vals, n, n, row_scale=bwd.row_scale, col_scale=bwd.col_scale)
+        assert A.core_kind() == "bf16-integer"
+        B = torch.randn(n, f, generator=g)
+        C = _poison_pads(ops.zeros_padded(n, f, "cuda"))
+        ops.spmm(A, _poison_pads(ops.to_padded(B.cuda())), C, 0.0)
+        _close(C, D.t() @ B.double())
+    finally:
+        ops.configure_core(**old)
+
+
 def test_integer_core_kernels_through_the_c_abi():
     """gather + scale + three-term bf16 split, the chunked bf16 multiply and the scaled row add, one by one."""
     if _native.lib().cagnet_core_gemm_int_available() != 1:
